@@ -1,0 +1,112 @@
+/*
+ * C ABI of libmircuda_b200.so — the sm_100a (B200) implementation of mircuda's
+ * quantized-matmul hot path.
+ *
+ * Every function below is `extern "C"`, takes plain pointers and sizes, and returns an
+ * `int` status unless noted: 0 = success, -1 = invalid argument (including "executed on a
+ * stream other than the plan's"), -2 = host allocation failure, -3 = the kernel reported a
+ * bounded wait that ran out on an earlier launch of this plan, anything else = a raw
+ * cudaError_t / CUresult. `stream` is a raw CUstream / cudaStream_t and must not be null.
+ *
+ * Plan-style operations keep the reference's contract: a plan is bound to the stream it
+ * was created on; `execute` only enqueues work (no host synchronisation, no allocation);
+ * operand buffers are caller-owned device memory and are not retained; a plan may be used
+ * by one thread at a time.
+ *
+ * Each declaration cites the reference interface it replaces (path inside the reference
+ * project : line). Entry points marked NEW have no counterpart there.
+ */
+#ifndef MIRCUDA_B200_H
+#define MIRCUDA_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Library identification: (major << 16) | (minor << 8) | patch. NEW. */
+uint32_t mircuda_b200_version(void);
+
+/* ------------------------------------------------------------------ MXFP8 quantizer ----
+ * bf16 [rows, columns] -> E4M3 codes [rows, columns] + one E8M0 scale per 32 columns,
+ * written straight into the 128x4-swizzled scale layout (`scales` must be zero-filled
+ * once by the caller; only real slots are written). columns % 32 == 0.
+ * Replaces the run-time-compiled kernel `mircuda_mxfp8_quantize_bf16`
+ * (kernels/mxfp8.cu:69-96) together with its launch in src/mxfp8/tensor_core.rs:140-158;
+ * an ahead-of-time launcher because the launch geometry differs from the reference's.
+ */
+int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output, void* scales,
+                                     uint32_t rows, uint32_t columns, void* stream);
+
+/* Row-major [rows, columns] E8M0 scales -> swizzled padded layout (one-time weight prep).
+ * Replaces `mircuda_mxfp8_swizzle_scales` (kernels/mxfp8.cu:98-109) and its launch in
+ * src/mxfp8/tensor_core.rs:89-107. `output` must be zero-filled by the caller. */
+int mircuda_b200_mxfp8_swizzle_scales(const void* input, void* output, uint32_t rows,
+                                      uint32_t columns, void* stream);
+
+/* --------------------------------------------------------- MXFP8 block-scaled GEMM ----
+ * C[m,n] (bf16) = A[m,k] (E4M3) . B[n,k]^T (E4M3), one UE8M0 scale per 32 K-elements of
+ * each operand in the swizzled layout, fp32 accumulation. k % 128 == 0.
+ * Replaces sys/native/mxfp8_sm120.cu:110-164, declared in
+ * sys/src/platform/cutlass/mxfp8.rs:11-30. */
+int mircuda_mxfp8_tc_create(int m, int n, int k, void* stream, void** output);
+size_t mircuda_mxfp8_tc_workspace_bytes(const void* plan);
+int mircuda_mxfp8_tc_execute(void* plan, void* stream, const void* a, const void* a_scales,
+                             const void* b, const void* b_scales, void* c);
+void mircuda_mxfp8_tc_destroy(void* plan);
+
+/* Weight-only MXFP8 (bf16 activations, row-major [n, k/32] E8M0 scales, weights as
+ * little-endian u32 words), any token count. Replaces `mircuda_mxfp8_bf16` and
+ * `mircuda_mxfp8_bf16_tiled` (kernels/mxfp8.cu:111-217) with their launches in
+ * src/mxfp8/matmul.rs:131-157. input_features % 32 == 0. */
+int mircuda_b200_mxfp8_bf16(const void* input, const void* weight, const void* scales,
+                            void* output, uint32_t tokens, uint32_t input_features,
+                            uint32_t output_features, void* stream);
+
+/* ----------------------------------------------------------- FP4 x FP4 GEMV (M = 1) ----
+ * y[n] (bf16) = alpha * sum_k e2m1(x) e2m1(W) sx sw; k % 64 == 0.
+ * Replaces sys/native/fp4_vector_sm120.cu:127-168, declared in
+ * sys/src/platform/cutlass/fp4/vector.rs:11-29. */
+int mircuda_fp4_vector_create(int n, int k, void* stream, void** output);
+int mircuda_fp4_vector_execute(void* plan, void* stream, const void* input,
+                               const void* input_scales, const void* weight,
+                               const void* weight_scales, void* output, float alpha);
+void mircuda_fp4_vector_destroy(void* plan);
+
+/* ------------------------------------------------------------ dense GEMV (M = 1) ----
+ * y = alpha W x + beta y, data_type 0 = f16, 1 = bf16, fp32 accumulation.
+ * Replaces sys/native/dense_vector_sm120.cu:147-175, declared in
+ * sys/src/platform/cutlass/dense/vector.rs:14-32. */
+int mircuda_dense_vector_create(int data_type, int n, int k, void* stream, void** output);
+int mircuda_dense_vector_execute(void* plan, void* stream, const void* input, const void* weight,
+                                 void* output, float alpha, float beta);
+void mircuda_dense_vector_destroy(void* plan);
+
+/* ------------------------------------------- bf16-activation x NVFP4-weight GEMV ----
+ * y[m,n] (bf16) = global_scale * sum_k x[m,k] e2m1(W[n,k]) ue4m3(sw[n,k/16]), m <= 8.
+ * NEW: the decode shape the benchmark configuration names; the reference serves it
+ * through its Marlin NVFP4 dense path (src/marlin/execute.rs:109-128), whose numerics
+ * (fp32 accumulation, global scale applied before the bf16 round) this follows.
+ * Weights and scales use the same layouts as mircuda_fp4_vector_*. k % 64 == 0. */
+int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* stream, void** output);
+int mircuda_b200_nvfp4_vector_execute(void* plan, void* stream, const void* input,
+                                      const void* weight, const void* weight_scales,
+                                      void* output, float global_scale);
+void mircuda_b200_nvfp4_vector_destroy(void* plan);
+
+/* bf16 [rows, k] -> NVFP4 codes [rows, k/2] + swizzled UE4M3 scales per 16, given the
+ * tensor's global scale (amax / 2688) in device memory. NEW: the reference has no NVFP4
+ * quantizer. `mircuda_b200_nvfp4_global_scale` computes that scale into *global_scale
+ * (a device float; also usable as the GEMV's global when read back). k % 64 == 0. */
+int mircuda_b200_nvfp4_global_scale(const void* input, size_t elements, void* global_scale,
+                                    void* stream);
+int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale, void* codes,
+                                     void* scales, uint32_t rows, uint32_t k, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* MIRCUDA_B200_H */

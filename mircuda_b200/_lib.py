@@ -1,0 +1,64 @@
+"""Loads ``libmircuda_b200.so`` and declares the C ABI of ``include/mircuda_b200.h``.
+
+There is no fallback: if the library is missing or a symbol cannot be resolved the import
+fails with an error that says how to build it.
+"""
+from __future__ import annotations
+
+import ctypes
+from pathlib import Path
+
+LIBRARY = Path(__file__).resolve().parent / "libmircuda_b200.so"
+
+_vp = ctypes.c_void_p
+_i = ctypes.c_int
+_u32 = ctypes.c_uint32
+_f = ctypes.c_float
+_sz = ctypes.c_size_t
+_vpp = ctypes.POINTER(ctypes.c_void_p)
+
+# name -> (restype, argtypes); mirrors include/mircuda_b200.h one to one.
+SIGNATURES = {
+    "mircuda_b200_version": (_u32, []),
+    "mircuda_b200_mxfp8_quantize_bf16": (_i, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mircuda_b200_mxfp8_swizzle_scales": (_i, [_vp, _vp, _u32, _u32, _vp]),
+    "mircuda_mxfp8_tc_create": (_i, [_i, _i, _i, _vp, _vpp]),
+    "mircuda_mxfp8_tc_workspace_bytes": (_sz, [_vp]),
+    "mircuda_mxfp8_tc_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
+    "mircuda_mxfp8_tc_destroy": (None, [_vp]),
+    "mircuda_b200_mxfp8_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mircuda_fp4_vector_create": (_i, [_i, _i, _vp, _vpp]),
+    "mircuda_fp4_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
+    "mircuda_fp4_vector_destroy": (None, [_vp]),
+    "mircuda_dense_vector_create": (_i, [_i, _i, _i, _vp, _vpp]),
+    "mircuda_dense_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _f]),
+    "mircuda_dense_vector_destroy": (None, [_vp]),
+    "mircuda_b200_nvfp4_vector_create": (_i, [_i, _i, _i, _vp, _vpp]),
+    "mircuda_b200_nvfp4_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _f]),
+    "mircuda_b200_nvfp4_vector_destroy": (None, [_vp]),
+    "mircuda_b200_nvfp4_global_scale": (_i, [_vp, _sz, _vp, _vp]),
+    "mircuda_b200_nvfp4_quantize_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
+}
+
+_handle = None
+
+
+def load() -> ctypes.CDLL:
+    global _handle
+    if _handle is not None:
+        return _handle
+    if not LIBRARY.exists():
+        raise ImportError(
+            f"{LIBRARY} is missing. Build it with `python -m mircuda_b200.build` "
+            "(needs nvcc; cross-compiles for sm_100a without a GPU). There is no CPU fallback."
+        )
+    handle = ctypes.CDLL(str(LIBRARY))
+    for name, (restype, argtypes) in SIGNATURES.items():
+        try:
+            function = getattr(handle, name)
+        except AttributeError as error:
+            raise ImportError(f"{LIBRARY} does not export {name}; rebuild it") from error
+        function.restype = restype
+        function.argtypes = argtypes
+    _handle = handle
+    return handle

@@ -1,0 +1,226 @@
+// FP4 x FP4 GEMV for decode (M = 1): y[N] = bf16(alpha * sum_blocks dot16 * sx * sw), E2M1
+// codes two per byte (even k in the low nibble), one UE4M3 scale per 16 K-elements in the
+// 128x4-swizzled layout. Replaces sys/native/fp4_vector_sm120.cu behind the same C entry
+// points; numerics follow that kernel (each 16-wide dot is formed exactly, then scaled by
+// the product of the two block scales and accumulated in fp32).
+//
+// The op streams 0.5625*N*K bytes once and is bound by HBM. Work is cut into tiles of
+// 128 rows (one scale row-tile) by 512 K-elements (eight whole 512-byte scale atoms), one CTA
+// per tile, so that every weight byte arrives through 16-byte loads with all of a tile's
+// loads in flight at once, every scale atom is fetched whole and coalesced, and there are
+// enough CTAs to fill the machine even for N = 4096. The activation slice a thread needs is
+// the same for all its rows, so it is decoded to f16x2 registers once. Products of two E2M1
+// values and sums of eight of them are exact in f16, so the inner loop is packed HFMA2.
+// K-slices of one row tile meet in a scratch array of per-slice partial sums; the CTA that
+// arrives last (a counter per row tile, no spinning) adds them in a fixed order, applies
+// alpha and writes bf16, which keeps results deterministic.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+#include <new>
+
+#include "fp4_codec.cuh"
+#include "layout.cuh"
+
+namespace mircuda_b200 {
+namespace fp4_vector {
+
+constexpr int kThreads = 256;
+constexpr int kTileRows = 128;
+constexpr int kTileK = 512;                       // elements per K-slice
+constexpr int kAtomsPerTile = kTileK / 64;        // scale atoms (4 columns of 16) per slice
+constexpr int kAtomStride = 512 + 8;              // padded in shared memory against bank conflicts
+constexpr int kRowSteps = kTileRows / (kThreads / 16);
+
+struct Plan {
+  int n;
+  int k;
+  int slices;
+  cudaStream_t stream;
+  float* partials;          // [slices][row_tiles * 128]
+  unsigned int* counters;   // [row_tiles], zero between launches
+};
+
+__global__ void __launch_bounds__(kThreads)
+kernel(const uint8_t* __restrict__ input, const uint8_t* __restrict__ input_scales,
+       const uint8_t* __restrict__ weight, const uint8_t* __restrict__ weight_scales,
+       __nv_bfloat16* __restrict__ output, float* __restrict__ partials,
+       unsigned int* __restrict__ counters, int n, int k, int slices, float alpha) {
+  __shared__ __align__(16) uint8_t shared_scales[kAtomsPerTile * kAtomStride];
+  __shared__ bool last_arrival;
+
+  const int row_tile = blockIdx.x;
+  const int slice = blockIdx.y;
+  const int k_begin = slice * kTileK;
+  const int atoms_k = k / 64;
+  const int lane16 = threadIdx.x & 15;
+  const int row_group = threadIdx.x >> 4;          // 0..15
+  const int element = k_begin + lane16 * 32;       // first of this thread's 32 K-elements
+  const bool active = element < k;
+
+  // Issue every weight load of the tile first: 8 x 16 bytes in flight per thread.
+  uint4 packed[kRowSteps];
+#pragma unroll
+  for (int step = 0; step < kRowSteps; ++step) {
+    const int row = row_tile * kTileRows + step * 16 + row_group;
+    packed[step] = make_uint4(0u, 0u, 0u, 0u);
+    if (active && row < n) {
+      packed[step] = load_streaming_16(weight + (static_cast<size_t>(row) * k + element) / 2);
+    }
+  }
+
+  // Whole scale atoms of this tile, coalesced: 8 atoms x 512 bytes = 256 threads x 16 bytes.
+  {
+    const int atom = threadIdx.x >> 5;
+    const int offset = (threadIdx.x & 31) * 16;
+    const int atom_column = k_begin / 64 + atom;
+    uint4 value = make_uint4(0u, 0u, 0u, 0u);
+    if (atom_column < atoms_k) {
+      value = __ldg(reinterpret_cast<const uint4*>(
+          weight_scales + (static_cast<size_t>(row_tile) * atoms_k + atom_column) * 512 + offset));
+    }
+    *reinterpret_cast<uint2*>(shared_scales + atom * kAtomStride + offset) =
+        make_uint2(value.x, value.y);
+    *reinterpret_cast<uint2*>(shared_scales + atom * kAtomStride + offset + 8) =
+        make_uint2(value.z, value.w);
+  }
+
+  // This thread's 32 activations (16 bytes) as f16x2 and their two block scales.
+  __half2 x[16];
+  float x_scale[2] = {0.0f, 0.0f};
+  if (active) {
+    const uint4 codes = __ldg(reinterpret_cast<const uint4*>(input + element / 2));
+    decode_e2m1x32(codes, x);
+    const int column = element / 16;
+    const uint16_t two = *reinterpret_cast<const uint16_t*>(
+        input_scales + scale_offset(0u, static_cast<uint32_t>(column), static_cast<uint32_t>(k / 16)));
+    x_scale[0] = decode_ue4m3(static_cast<uint8_t>(two & 0xffu));
+    x_scale[1] = decode_ue4m3(static_cast<uint8_t>(two >> 8));
+  } else {
+#pragma unroll
+    for (int pair = 0; pair < 16; ++pair) x[pair] = __float2half2_rn(0.0f);
+  }
+  __syncthreads();
+
+  const int scale_atom = lane16 >> 1;               // 64 elements per atom column group
+  const int scale_byte = (lane16 & 1) * 2;          // two of its four columns
+#pragma unroll
+  for (int step = 0; step < kRowSteps; ++step) {
+    const int row_in_tile = step * 16 + row_group;
+    __half2 w[16];
+    decode_e2m1x32(packed[step], w);
+    float sum = 0.0f;
+#pragma unroll
+    for (int block = 0; block < 2; ++block) {
+      __half2 dot = __float2half2_rn(0.0f);
+#pragma unroll
+      for (int pair = 0; pair < 8; ++pair) dot = __hfma2(x[block * 8 + pair], w[block * 8 + pair], dot);
+      const uint8_t code = shared_scales[scale_atom * kAtomStride + (row_in_tile & 31) * 16 +
+                                         (row_in_tile >> 5) * 4 + scale_byte + block];
+      const float2 halves = __half22float2(dot);
+      sum = fmaf(halves.x + halves.y, x_scale[block] * decode_ue4m3(code), sum);
+    }
+#pragma unroll
+    for (int offset = 8; offset > 0; offset >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, offset);
+    if (lane16 == 0) {
+      const int row = row_tile * kTileRows + row_in_tile;
+      if (slices == 1) {
+        if (row < n) output[row] = __float2bfloat16_rn(sum * alpha);
+      } else {
+        partials[static_cast<size_t>(slice) * gridDim.x * kTileRows + row] = sum;
+      }
+    }
+  }
+  if (slices == 1) return;
+
+  // Last-arriving slice of this row tile reduces in slice order. No CTA waits on another.
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int arrived = atomicAdd(&counters[row_tile], 1u);
+    last_arrival = arrived == static_cast<unsigned int>(slices - 1);
+    if (last_arrival) counters[row_tile] = 0u;
+  }
+  __syncthreads();
+  if (!last_arrival) return;
+  __threadfence();
+  if (threadIdx.x < kTileRows) {
+    const int row = row_tile * kTileRows + threadIdx.x;
+    float total = 0.0f;
+    for (int part = 0; part < slices; ++part) {
+      total += __ldcg(partials + static_cast<size_t>(part) * gridDim.x * kTileRows + row);
+    }
+    if (row < n) output[row] = __float2bfloat16_rn(total * alpha);
+  }
+}
+
+}  // namespace fp4_vector
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_fp4_vector_create(int n, int k, void* stream, void** output) {
+  using namespace mircuda_b200::fp4_vector;
+  if (n <= 0 || k <= 0 || k % 64 != 0 || stream == nullptr || output == nullptr) return -1;
+  auto* plan = new (std::nothrow) Plan{};
+  if (plan == nullptr) return -2;
+  plan->n = n;
+  plan->k = k;
+  plan->slices = (k + kTileK - 1) / kTileK;
+  plan->stream = static_cast<cudaStream_t>(stream);
+  const size_t row_tiles = (static_cast<size_t>(n) + kTileRows - 1) / kTileRows;
+  int status = 0;
+  if (plan->slices > 1) {
+    status = static_cast<int>(cudaMallocAsync(
+        reinterpret_cast<void**>(&plan->partials),
+        static_cast<size_t>(plan->slices) * row_tiles * kTileRows * sizeof(float), plan->stream));
+    if (status == 0) {
+      status = static_cast<int>(cudaMallocAsync(reinterpret_cast<void**>(&plan->counters),
+                                                row_tiles * sizeof(unsigned int), plan->stream));
+    }
+    if (status == 0) {
+      status = static_cast<int>(
+          cudaMemsetAsync(plan->counters, 0, row_tiles * sizeof(unsigned int), plan->stream));
+    }
+  }
+  if (status != 0) {
+    if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
+    if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
+    delete plan;
+    return status;
+  }
+  *output = plan;
+  return 0;
+}
+
+extern "C" int mircuda_fp4_vector_execute(void* raw, void* stream, const void* input,
+                                          const void* input_scales, const void* weight,
+                                          const void* weight_scales, void* output, float alpha) {
+  using namespace mircuda_b200::fp4_vector;
+  if (raw == nullptr || stream == nullptr || input == nullptr || input_scales == nullptr ||
+      weight == nullptr || weight_scales == nullptr || output == nullptr) {
+    return -1;
+  }
+  auto* plan = static_cast<Plan*>(raw);
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  if (cuda_stream != plan->stream) return -1;
+  if (((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(weight) |
+        reinterpret_cast<uintptr_t>(weight_scales)) & 15u) != 0u) {
+    return -1;
+  }
+  const dim3 grid((plan->n + kTileRows - 1) / kTileRows, plan->slices);
+  kernel<<<grid, kThreads, 0, cuda_stream>>>(
+      static_cast<const uint8_t*>(input), static_cast<const uint8_t*>(input_scales),
+      static_cast<const uint8_t*>(weight), static_cast<const uint8_t*>(weight_scales),
+      static_cast<__nv_bfloat16*>(output), plan->partials, plan->counters, plan->n, plan->k,
+      plan->slices, alpha);
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+extern "C" void mircuda_fp4_vector_destroy(void* raw) {
+  auto* plan = static_cast<mircuda_b200::fp4_vector::Plan*>(raw);
+  if (plan == nullptr) return;
+  if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
+  if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
+  delete plan;
+}

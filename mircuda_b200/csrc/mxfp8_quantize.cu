@@ -1,0 +1,168 @@
+// bf16 -> MXFP8 activation quantizer and the scale-layout conversion.
+//
+// Semantics follow the reference kernel `mircuda_mxfp8_quantize_bf16`
+// (kernels/mxfp8.cu:69-96) bit for bit on finite inputs; the geometry does not: the
+// reference runs one 32-thread block per 32-element group with 2-byte loads, this kernel
+// streams 16-byte vectors (8 bf16 per thread, 4 threads per group) and writes the four
+// scale bytes of an aligned group quartet as one 32-bit store into the swizzled atom.
+// The kernel is bound by HBM: 2 bytes read and 1 + 1/32 bytes written per element.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+#include "layout.cuh"
+
+namespace mircuda_b200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kVectorsPerThread = 4;
+
+// Exponent byte of the block scale from the block's largest bf16 magnitude (15 bits).
+// ceil(log2(amax / 448)) + 127 with 448 = 1.75 * 2^8: for amax = m * 2^e, 1 <= m < 2, this
+// is e - 8 + 127, plus one when m > 1.75 (mantissa field above 0x60). Zero and subnormal
+// magnitudes land on the clamp at 0, as max(amax / 448, 2^-127) does in the reference.
+__device__ __forceinline__ uint32_t scale_exponent(uint32_t magnitude_bits) {
+  const uint32_t exponent = magnitude_bits >> 7;
+  if (exponent == 0u) return 0u;
+  const int biased = static_cast<int>(exponent) - 8 + ((magnitude_bits & 0x7fu) > 0x60u ? 1 : 0);
+  return static_cast<uint32_t>(max(0, min(254, biased)));
+}
+
+// 2^(127 - exponent_byte) as an fp32 (the reciprocal of the block scale); 2^-127 is the
+// subnormal 0x00400000.
+__device__ __forceinline__ float inverse_scale(uint32_t exponent_byte) {
+  const int power = 127 - static_cast<int>(exponent_byte);
+  const uint32_t bits = power >= -126 ? static_cast<uint32_t>(power + 127) << 23 : 0x00400000u;
+  return __uint_as_float(bits);
+}
+
+__device__ __forceinline__ uint32_t magnitude_for_max(uint32_t half_bits) {
+  const uint32_t magnitude = half_bits & 0x7fffu;
+  return magnitude > 0x7f80u ? 0u : magnitude;  // NaN takes no part, as with fmaxf
+}
+
+// Two bf16 (packed in a u32, low half first) times `inverse` -> two E4M3 codes (low byte first).
+__device__ __forceinline__ uint32_t encode_pair(uint32_t packed, float inverse) {
+  const float low = __uint_as_float(packed << 16) * inverse;
+  const float high = __uint_as_float(packed & 0xffff0000u) * inverse;
+  return static_cast<uint32_t>(
+      __nv_cvt_float2_to_fp8x2(make_float2(low, high), __NV_SATFINITE, __NV_E4M3));
+}
+
+template <bool kPackedScales>
+__global__ void __launch_bounds__(kThreads)
+quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
+                uint8_t* __restrict__ scales, uint32_t rows, uint32_t columns) {
+  const uint32_t vectors_per_row = columns / 8u;
+  const uint32_t groups_per_row = columns / 32u;
+  const uint64_t vectors = static_cast<uint64_t>(rows) * vectors_per_row;
+  const uint64_t first =
+      static_cast<uint64_t>(blockIdx.x) * (kThreads * kVectorsPerThread) + threadIdx.x;
+
+  uint4 values[kVectorsPerThread];
+#pragma unroll
+  for (int item = 0; item < kVectorsPerThread; ++item) {
+    const uint64_t vector = first + static_cast<uint64_t>(item) * kThreads;
+    values[item] = vector < vectors ? __ldg(input + vector) : make_uint4(0u, 0u, 0u, 0u);
+  }
+
+#pragma unroll
+  for (int item = 0; item < kVectorsPerThread; ++item) {
+    const uint64_t vector = first + static_cast<uint64_t>(item) * kThreads;
+    const uint4 v = values[item];
+    uint32_t maximum = max(max(magnitude_for_max(v.x), magnitude_for_max(v.x >> 16)),
+                           max(magnitude_for_max(v.y), magnitude_for_max(v.y >> 16)));
+    maximum = max(maximum, max(max(magnitude_for_max(v.z), magnitude_for_max(v.z >> 16)),
+                               max(magnitude_for_max(v.w), magnitude_for_max(v.w >> 16))));
+    maximum = max(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
+    maximum = max(maximum, __shfl_xor_sync(0xffffffffu, maximum, 2));
+    const uint32_t exponent = scale_exponent(maximum);
+    const float inverse = inverse_scale(exponent);
+    const uint32_t low = encode_pair(v.x, inverse) | (encode_pair(v.y, inverse) << 16);
+    const uint32_t high = encode_pair(v.z, inverse) | (encode_pair(v.w, inverse) << 16);
+    if (vector < vectors) output[vector] = make_uint2(low, high);
+
+    // One scale byte per 4-thread group. A warp holds 8 consecutive groups; when rows are a
+    // multiple of 128 columns those are two aligned quartets whose bytes are adjacent in the
+    // swizzled atom, so lanes 0 and 16 each write one 32-bit word.
+    const uint64_t group = vector / 4u;
+    const uint32_t row = static_cast<uint32_t>(group / groups_per_row);
+    const uint32_t group_in_row = static_cast<uint32_t>(group % groups_per_row);
+    if constexpr (kPackedScales) {
+      const uint32_t lane = threadIdx.x & 31u;
+      const uint32_t base = lane & 16u;
+      const uint32_t word = __shfl_sync(0xffffffffu, exponent, base) |
+                            (__shfl_sync(0xffffffffu, exponent, base + 4u) << 8) |
+                            (__shfl_sync(0xffffffffu, exponent, base + 8u) << 16) |
+                            (__shfl_sync(0xffffffffu, exponent, base + 12u) << 24);
+      if ((lane & 15u) == 0u && vector < vectors) {
+        *reinterpret_cast<uint32_t*>(scales + scale_offset(row, group_in_row, groups_per_row)) =
+            word;
+      }
+    } else {
+      if ((threadIdx.x & 3u) == 0u && vector < vectors) {
+        scales[scale_offset(row, group_in_row, groups_per_row)] = static_cast<uint8_t>(exponent);
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256)
+swizzle_scales_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output,
+                      uint32_t rows, uint32_t columns) {
+  const uint64_t index = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (index >= static_cast<uint64_t>(rows) * columns) return;
+  const uint32_t row = static_cast<uint32_t>(index / columns);
+  const uint32_t column = static_cast<uint32_t>(index % columns);
+  output[scale_offset(row, column, columns)] = input[index];
+}
+
+}  // namespace
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output, void* scales,
+                                                uint32_t rows, uint32_t columns, void* stream) {
+  using namespace mircuda_b200;
+  if (input == nullptr || output == nullptr || scales == nullptr || stream == nullptr ||
+      rows == 0u || columns == 0u || columns % 32u != 0u) {
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(input) & 15u) != 0u ||
+      (reinterpret_cast<uintptr_t>(output) & 7u) != 0u ||
+      (reinterpret_cast<uintptr_t>(scales) & 3u) != 0u) {
+    return -1;
+  }
+  const uint64_t vectors = static_cast<uint64_t>(rows) * (columns / 8u);
+  const uint64_t per_block = kThreads * kVectorsPerThread;
+  const uint64_t blocks = (vectors + per_block - 1u) / per_block;
+  if (blocks > 0x7fffffffull) return -1;
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  if (columns % 128u == 0u) {
+    quantize_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
+        static_cast<const uint4*>(input), static_cast<uint2*>(output),
+        static_cast<uint8_t*>(scales), rows, columns);
+  } else {
+    quantize_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
+        static_cast<const uint4*>(input), static_cast<uint2*>(output),
+        static_cast<uint8_t*>(scales), rows, columns);
+  }
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+extern "C" int mircuda_b200_mxfp8_swizzle_scales(const void* input, void* output, uint32_t rows,
+                                                 uint32_t columns, void* stream) {
+  using namespace mircuda_b200;
+  if (input == nullptr || output == nullptr || stream == nullptr || rows == 0u || columns == 0u) {
+    return -1;
+  }
+  const uint64_t elements = static_cast<uint64_t>(rows) * columns;
+  const uint64_t blocks = (elements + 255u) / 256u;
+  if (blocks > 0x7fffffffull) return -1;
+  swizzle_scales_kernel<<<static_cast<unsigned int>(blocks), 256, 0,
+                          static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint8_t*>(input), static_cast<uint8_t*>(output), rows, columns);
+  return static_cast<int>(cudaPeekAtLastError());
+}

@@ -1,0 +1,153 @@
+// bf16 -> NVFP4 quantizer (E2M1 codes, one UE4M3 scale per 16 K-elements, per-tensor fp32
+// global scale). The reference has no such quantizer; the rule implemented here is
+//   global = amax_tensor / (448 * 6)              (1.0 for an all-zero tensor)
+//   s_blk  = rne_ue4m3(amax_blk / (6 * global))
+//   code   = rne_e2m1(x / (ue4m3(s_blk) * global)), saturating at +-6; 0 when s_blk == 0
+// with every operation in round-to-nearest fp32. Conversions use the sm_100a cvt
+// instructions. The kernel is bound by HBM: 2 bytes in, 0.5625 bytes out per element.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+#include "fp4_codec.cuh"
+#include "layout.cuh"
+
+namespace mircuda_b200 {
+namespace {
+
+__device__ __forceinline__ uint32_t magnitude_bits(uint32_t half_bits) {
+  const uint32_t magnitude = half_bits & 0x7fffu;
+  return magnitude > 0x7f80u ? 0u : magnitude;  // NaN takes no part in amax
+}
+
+__device__ __forceinline__ uint32_t max_magnitude(const uint4& v) {
+  uint32_t result = max(max(magnitude_bits(v.x), magnitude_bits(v.x >> 16)),
+                        max(magnitude_bits(v.y), magnitude_bits(v.y >> 16)));
+  return max(result, max(max(magnitude_bits(v.z), magnitude_bits(v.z >> 16)),
+                         max(magnitude_bits(v.w), magnitude_bits(v.w >> 16))));
+}
+
+// Largest |x| as bf16 magnitude bits, combined across the grid with an integer atomic max.
+__global__ void __launch_bounds__(256)
+amax_kernel(const uint4* __restrict__ input, size_t vectors, const uint16_t* __restrict__ tail,
+            size_t tail_elements, unsigned int* __restrict__ result) {
+  uint32_t maximum = 0u;
+  for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < vectors;
+       index += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    maximum = max(maximum, max_magnitude(__ldg(input + index)));
+  }
+  if (blockIdx.x == 0 && threadIdx.x < tail_elements) {
+    maximum = max(maximum, magnitude_bits(tail[threadIdx.x]));
+  }
+#pragma unroll
+  for (int offset = 16; offset > 0; offset >>= 1) {
+    maximum = max(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
+  }
+  if ((threadIdx.x & 31) == 0 && maximum != 0u) atomicMax(result, maximum);
+}
+
+__global__ void finish_global_scale(unsigned int* word) {
+  const uint32_t magnitude = *word;  // bf16 bits of the tensor amax
+  const float amax = __uint_as_float(magnitude << 16);
+  const float global = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
+  *reinterpret_cast<float*>(word) = global;
+}
+
+__device__ __forceinline__ uint32_t encode_e2m1_pair(float low, float high) {
+  uint16_t packed;
+  asm("{\n\t"
+      ".reg .b8 byte;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 byte, %2, %1;\n\t"
+      "cvt.u16.u8 %0, byte;\n\t"
+      "}\n"
+      : "=h"(packed)
+      : "f"(low), "f"(high));
+  return packed;
+}
+
+// One thread per 16-element block: two 16-byte loads, one 8-byte store, one scale byte.
+__global__ void __launch_bounds__(256)
+quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
+                uint2* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t rows,
+                uint32_t k) {
+  const uint32_t blocks_per_row = k / 16u;
+  const size_t block = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (block >= static_cast<size_t>(rows) * blocks_per_row) return;
+  const uint4 first = __ldg(input + block * 2u);
+  const uint4 second = __ldg(input + block * 2u + 1u);
+  const float global = *global_scale;
+  const uint32_t magnitude = max(max_magnitude(first), max_magnitude(second));
+  const float block_max = __uint_as_float(magnitude << 16);
+  const float requested = __fdiv_rn(block_max, __fmul_rn(6.0f, global));
+  uint8_t scale_code = 0u;
+  if (requested > 0.0f) {
+    scale_code = static_cast<uint8_t>(
+        __nv_cvt_float_to_fp8(requested, __NV_SATFINITE, __NV_E4M3) & 0x7fu);
+  }
+  const float denominator = __fmul_rn(decode_ue4m3(scale_code), global);
+  const uint32_t words[8] = {first.x, first.y, first.z, first.w,
+                             second.x, second.y, second.z, second.w};
+  uint32_t out[2] = {0u, 0u};
+  if (scale_code != 0u) {
+#pragma unroll
+    for (int word = 0; word < 8; ++word) {
+      const float low = __fdiv_rn(__uint_as_float(words[word] << 16), denominator);
+      const float high = __fdiv_rn(__uint_as_float(words[word] & 0xffff0000u), denominator);
+      out[word / 4] |= encode_e2m1_pair(low, high) << ((word % 4) * 8);
+    }
+  }
+  codes[block] = make_uint2(out[0], out[1]);
+  const uint32_t row = static_cast<uint32_t>(block / blocks_per_row);
+  const uint32_t column = static_cast<uint32_t>(block % blocks_per_row);
+  scales[scale_offset(row, column, blocks_per_row)] = scale_code;
+}
+
+}  // namespace
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_nvfp4_global_scale(const void* input, size_t elements,
+                                               void* global_scale, void* stream) {
+  using namespace mircuda_b200;
+  if (input == nullptr || global_scale == nullptr || stream == nullptr || elements == 0u) return -1;
+  if ((reinterpret_cast<uintptr_t>(input) & 15u) != 0u ||
+      (reinterpret_cast<uintptr_t>(global_scale) & 3u) != 0u) {
+    return -1;
+  }
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  int status = static_cast<int>(cudaMemsetAsync(global_scale, 0, sizeof(float), cuda_stream));
+  if (status != 0) return status;
+  const size_t vectors = elements / 8u;
+  const size_t tail = elements % 8u;
+  size_t blocks = (vectors + 255u) / 256u;
+  if (blocks > 148u * 8u) blocks = 148u * 8u;
+  if (blocks == 0u) blocks = 1u;
+  amax_kernel<<<static_cast<unsigned int>(blocks), 256, 0, cuda_stream>>>(
+      static_cast<const uint4*>(input), vectors,
+      static_cast<const uint16_t*>(input) + vectors * 8u, tail,
+      static_cast<unsigned int*>(global_scale));
+  finish_global_scale<<<1, 1, 0, cuda_stream>>>(static_cast<unsigned int*>(global_scale));
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+extern "C" int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale,
+                                                void* codes, void* scales, uint32_t rows,
+                                                uint32_t k, void* stream) {
+  using namespace mircuda_b200;
+  if (input == nullptr || global_scale == nullptr || codes == nullptr || scales == nullptr ||
+      stream == nullptr || rows == 0u || k == 0u || k % 64u != 0u) {
+    return -1;
+  }
+  if ((reinterpret_cast<uintptr_t>(input) & 15u) != 0u ||
+      (reinterpret_cast<uintptr_t>(codes) & 7u) != 0u) {
+    return -1;
+  }
+  const size_t blocks = static_cast<size_t>(rows) * (k / 16u);
+  const size_t grid = (blocks + 255u) / 256u;
+  if (grid > 0x7fffffffull) return -1;
+  quantize_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
+      static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, k);
+  return static_cast<int>(cudaPeekAtLastError());
+}
