@@ -339,7 +339,7 @@ def run_gpu(args) -> None:
             },
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None, "kernel": "mxfp8_gemm::kernel",
+                "frac": achieved / peak, "traffic": None, "kernel": "mxfp8_gemm_kernel",
                 "peak_source": peak_note, "frac_of_nominal_fp8_4500": achieved / 4500.0,
                 "per_layer_tflops": {
                     name: 2.0 * TOKENS * next(l for l in layers if l["name"] == name)["local_n"]
@@ -360,6 +360,7 @@ def run_gpu(args) -> None:
 
 
 def main() -> None:
+    global SHAPES
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
     parser.add_argument("--steps", type=int, default=20)
@@ -370,7 +371,6 @@ def main() -> None:
     parser.add_argument("--layers", default=",".join(name for name, _, _ in SHAPES),
                         help="comma-separated subset of the four linears (profiling runs)")
     args = parser.parse_args()
-    global SHAPES
     chosen = args.layers.split(",")
     SHAPES = [shape for shape in SHAPES if shape[0] in chosen]
     if not SHAPES:

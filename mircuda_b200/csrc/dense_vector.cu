@@ -71,7 +71,7 @@ __device__ __forceinline__ float dot8(const uint4& w, const uint4& x, float sum)
 
 template <typename T>
 __global__ void __launch_bounds__(kWarps * 32)
-kernel(const T* __restrict__ input, const T* __restrict__ weight, T* __restrict__ output, int n,
+dense_vector_kernel(const T* __restrict__ input, const T* __restrict__ weight, T* __restrict__ output, int n,
        int k, float alpha, float beta) {
   const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
@@ -152,7 +152,7 @@ int launch(const Plan* plan, const void* input, const void* weight, void* output
            float beta) {
   const int rows_per_block = kWarps * kRowsPerWarp;
   const int blocks = (plan->n + rows_per_block - 1) / rows_per_block;
-  kernel<T><<<blocks, kWarps * 32, 0, plan->stream>>>(
+  dense_vector_kernel<T><<<blocks, kWarps * 32, 0, plan->stream>>>(
       static_cast<const T*>(input), static_cast<const T*>(weight), static_cast<T*>(output),
       plan->n, plan->k, alpha, beta);
   return static_cast<int>(cudaPeekAtLastError());

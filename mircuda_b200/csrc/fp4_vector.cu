@@ -44,7 +44,7 @@ struct Plan {
 };
 
 __global__ void __launch_bounds__(kThreads)
-kernel(const uint8_t* __restrict__ input, const uint8_t* __restrict__ input_scales,
+fp4_vector_kernel(const uint8_t* __restrict__ input, const uint8_t* __restrict__ input_scales,
        const uint8_t* __restrict__ weight, const uint8_t* __restrict__ weight_scales,
        __nv_bfloat16* __restrict__ output, float* __restrict__ partials,
        unsigned int* __restrict__ counters, int n, int k, int slices, float alpha) {
@@ -209,7 +209,7 @@ extern "C" int mircuda_fp4_vector_execute(void* raw, void* stream, const void* i
     return -1;
   }
   const dim3 grid((plan->n + kTileRows - 1) / kTileRows, plan->slices);
-  kernel<<<grid, kThreads, 0, cuda_stream>>>(
+  fp4_vector_kernel<<<grid, kThreads, 0, cuda_stream>>>(
       static_cast<const uint8_t*>(input), static_cast<const uint8_t*>(input_scales),
       static_cast<const uint8_t*>(weight), static_cast<const uint8_t*>(weight_scales),
       static_cast<__nv_bfloat16*>(output), plan->partials, plan->counters, plan->n, plan->k,

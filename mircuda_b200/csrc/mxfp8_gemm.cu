@@ -60,7 +60,7 @@ struct Layout {
 
 template <uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
-kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
        const uint8_t* __restrict__ scales_a, const uint8_t* __restrict__ scales_b,
        __nv_bfloat16* __restrict__ c, uint32_t m, uint32_t n, uint32_t k,
        uint32_t* __restrict__ status) {
@@ -291,7 +291,7 @@ struct Plan {
 template <uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
 int launch(Plan* plan, const void* a_scales, const void* b_scales, void* c) {
   using L = Layout<BN, STAGES, ACC_STAGES>;
-  auto function = kernel<BN, STAGES, ACC_STAGES>;
+  auto function = mxfp8_gemm_kernel<BN, STAGES, ACC_STAGES>;
   static thread_local int configured_device = -1;
   if (configured_device != plan->device) {
     const int status = static_cast<int>(cudaFuncSetAttribute(

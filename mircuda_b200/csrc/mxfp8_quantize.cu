@@ -54,7 +54,7 @@ __device__ __forceinline__ uint32_t encode_pair(uint32_t packed, float inverse) 
 
 template <bool kPackedScales>
 __global__ void __launch_bounds__(kThreads)
-quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
+mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
                 uint8_t* __restrict__ scales, uint32_t rows, uint32_t columns) {
   const uint32_t vectors_per_row = columns / 8u;
   const uint32_t groups_per_row = columns / 32u;
@@ -111,7 +111,7 @@ quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
 }
 
 __global__ void __launch_bounds__(256)
-swizzle_scales_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output,
+mxfp8_swizzle_scales_kernel(const uint8_t* __restrict__ input, uint8_t* __restrict__ output,
                       uint32_t rows, uint32_t columns) {
   const uint64_t index = static_cast<uint64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (index >= static_cast<uint64_t>(rows) * columns) return;
@@ -141,11 +141,11 @@ extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output,
   if (blocks > 0x7fffffffull) return -1;
   auto cuda_stream = static_cast<cudaStream_t>(stream);
   if (columns % 128u == 0u) {
-    quantize_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
+    mxfp8_quantize_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
         static_cast<const uint4*>(input), static_cast<uint2*>(output),
         static_cast<uint8_t*>(scales), rows, columns);
   } else {
-    quantize_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
+    mxfp8_quantize_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
         static_cast<const uint4*>(input), static_cast<uint2*>(output),
         static_cast<uint8_t*>(scales), rows, columns);
   }
@@ -161,7 +161,7 @@ extern "C" int mircuda_b200_mxfp8_swizzle_scales(const void* input, void* output
   const uint64_t elements = static_cast<uint64_t>(rows) * columns;
   const uint64_t blocks = (elements + 255u) / 256u;
   if (blocks > 0x7fffffffull) return -1;
-  swizzle_scales_kernel<<<static_cast<unsigned int>(blocks), 256, 0,
+  mxfp8_swizzle_scales_kernel<<<static_cast<unsigned int>(blocks), 256, 0,
                           static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint8_t*>(input), static_cast<uint8_t*>(output), rows, columns);
   return static_cast<int>(cudaPeekAtLastError());

@@ -30,7 +30,7 @@ __device__ __forceinline__ float2 decode_e4m3x2(uint32_t two_codes) {
 }
 
 __global__ void __launch_bounds__(kWarps * 32)
-weight_only_kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __restrict__ weight,
+mxfp8_weight_only_kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __restrict__ weight,
                    const uint8_t* __restrict__ scales, __nv_bfloat16* __restrict__ output,
                    uint32_t tokens, uint32_t k, uint32_t n) {
   const uint32_t lane = threadIdx.x & 31u;
@@ -123,7 +123,7 @@ extern "C" int mircuda_b200_mxfp8_bf16(const void* input, const void* weight, co
   }
   const dim3 grid((output_features + kWarps - 1) / kWarps, (tokens + kTokenTile - 1) / kTokenTile);
   if (grid.y > 65535u) return -1;
-  weight_only_kernel<<<grid, kWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
+  mxfp8_weight_only_kernel<<<grid, kWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(input), static_cast<const uint8_t*>(weight),
       static_cast<const uint8_t*>(scales), static_cast<__nv_bfloat16*>(output), tokens,
       input_features, output_features);

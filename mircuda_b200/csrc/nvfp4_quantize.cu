@@ -31,7 +31,7 @@ __device__ __forceinline__ uint32_t max_magnitude(const uint4& v) {
 
 // Largest |x| as bf16 magnitude bits, combined across the grid with an integer atomic max.
 __global__ void __launch_bounds__(256)
-amax_kernel(const uint4* __restrict__ input, size_t vectors, const uint16_t* __restrict__ tail,
+nvfp4_amax_kernel(const uint4* __restrict__ input, size_t vectors, const uint16_t* __restrict__ tail,
             size_t tail_elements, unsigned int* __restrict__ result) {
   uint32_t maximum = 0u;
   for (size_t index = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; index < vectors;
@@ -48,7 +48,7 @@ amax_kernel(const uint4* __restrict__ input, size_t vectors, const uint16_t* __r
   if ((threadIdx.x & 31) == 0 && maximum != 0u) atomicMax(result, maximum);
 }
 
-__global__ void finish_global_scale(unsigned int* word) {
+__global__ void nvfp4_finish_global_scale_kernel(unsigned int* word) {
   const uint32_t magnitude = *word;  // bf16 bits of the tensor amax
   const float amax = __uint_as_float(magnitude << 16);
   const float global = amax > 0.0f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
@@ -69,7 +69,7 @@ __device__ __forceinline__ uint32_t encode_e2m1_pair(float low, float high) {
 
 // One thread per 16-element block: two 16-byte loads, one 8-byte store, one scale byte.
 __global__ void __launch_bounds__(256)
-quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
+nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
                 uint2* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t rows,
                 uint32_t k) {
   const uint32_t blocks_per_row = k / 16u;
@@ -123,11 +123,11 @@ extern "C" int mircuda_b200_nvfp4_global_scale(const void* input, size_t element
   size_t blocks = (vectors + 255u) / 256u;
   if (blocks > 148u * 8u) blocks = 148u * 8u;
   if (blocks == 0u) blocks = 1u;
-  amax_kernel<<<static_cast<unsigned int>(blocks), 256, 0, cuda_stream>>>(
+  nvfp4_amax_kernel<<<static_cast<unsigned int>(blocks), 256, 0, cuda_stream>>>(
       static_cast<const uint4*>(input), vectors,
       static_cast<const uint16_t*>(input) + vectors * 8u, tail,
       static_cast<unsigned int*>(global_scale));
-  finish_global_scale<<<1, 1, 0, cuda_stream>>>(static_cast<unsigned int*>(global_scale));
+  nvfp4_finish_global_scale_kernel<<<1, 1, 0, cuda_stream>>>(static_cast<unsigned int*>(global_scale));
   return static_cast<int>(cudaPeekAtLastError());
 }
 
@@ -146,7 +146,7 @@ extern "C" int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* g
   const size_t blocks = static_cast<size_t>(rows) * (k / 16u);
   const size_t grid = (blocks + 255u) / 256u;
   if (grid > 0x7fffffffull) return -1;
-  quantize_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+  nvfp4_quantize_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
       static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, k);
   return static_cast<int>(cudaPeekAtLastError());

@@ -93,7 +93,7 @@ __device__ __forceinline__ uint32_t scale_multiplier(uint8_t code) {
 }
 
 __global__ void __launch_bounds__(kThreads)
-kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __restrict__ weight,
+nvfp4_vector_kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __restrict__ weight,
        const uint8_t* __restrict__ weight_scales, __nv_bfloat16* __restrict__ output,
        float* __restrict__ partials, unsigned int* __restrict__ counters, int m, int n, int k,
        int slices, float global_scale) {
@@ -319,7 +319,7 @@ extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const 
     return -1;
   }
   const dim3 grid((plan->n + kTileRows - 1) / kTileRows, plan->slices);
-  kernel<<<grid, kThreads, 0, cuda_stream>>>(
+  nvfp4_vector_kernel<<<grid, kThreads, 0, cuda_stream>>>(
       static_cast<const __nv_bfloat16*>(input), static_cast<const uint8_t*>(weight),
       static_cast<const uint8_t*>(weight_scales), static_cast<__nv_bfloat16*>(output),
       plan->partials, plan->counters, plan->m, plan->n, plan->k, plan->slices, global_scale);
