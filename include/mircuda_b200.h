@@ -75,6 +75,22 @@ int mircuda_fp4_vector_execute(void* plan, void* stream, const void* input,
                                const void* weight_scales, void* output, float alpha);
 void mircuda_fp4_vector_destroy(void* plan);
 
+/* The same FP4 x FP4 GEMV without a plan and without any allocation. This entry point has
+ * no counterpart in the reference. It is for hosts that do not allow this library to call
+ * the CUDA allocator (all device memory already belongs to the host's own arena, or the
+ * caller only owns raw pointers inside someone else's pool): the cross-slice scratch that
+ * mircuda_fp4_vector_create would allocate lives in a fixed 1 MiB + 4 KiB device array inside
+ * the library instead, which every GPU that loads the library holds until the process ends.
+ * Limits: ceil(k / 512) * ceil(n / 128) * 128 <= 262144 and n <= 131072; a larger shape
+ * returns -4 and launches nothing. The first call on each device looks up the array's
+ * device address (with that device current); make that first call outside any stream
+ * capture. All calls on a device share the one array: it keeps the previous call's contents
+ * (the call clears the part that must start at zero), and two calls whose kernels overlap
+ * on the GPU, e.g. on different streams, race. */
+int mircuda_b200_fp4_vector_execute_static(int n, int k, void* stream, const void* input,
+                                           const void* input_scales, const void* weight,
+                                           const void* weight_scales, void* output, float alpha);
+
 /* ------------------------------------------------------------ dense GEMV (M = 1) ----
  * y = alpha W x + beta y, data_type 0 = f16, 1 = bf16, fp32 accumulation.
  * Replaces sys/native/dense_vector_sm120.cu:147-175, declared in

@@ -30,6 +30,7 @@ SIGNATURES = {
     "mircuda_fp4_vector_create": (_i, [_i, _i, _vp, _vpp]),
     "mircuda_fp4_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "mircuda_fp4_vector_destroy": (None, [_vp]),
+    "mircuda_b200_fp4_vector_execute_static": (_i, [_i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "mircuda_dense_vector_create": (_i, [_i, _i, _i, _vp, _vpp]),
     "mircuda_dense_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _f]),
     "mircuda_dense_vector_destroy": (None, [_vp]),

@@ -19,6 +19,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <mutex>
 #include <new>
 
 #include "fp4_codec.cuh"
@@ -223,4 +224,100 @@ extern "C" void mircuda_fp4_vector_destroy(void* raw) {
   if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
   if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
   delete plan;
+}
+
+// ------------------------------------------------------------------------------------------
+// Allocation-free variant.
+//
+// Some hosts may not let this library call the CUDA allocator at all: a serving process that
+// handed every byte of device memory to its own arena at start-up (a later cudaMalloc would
+// fail or evict), or a caller that only owns raw pointers inside somebody else's memory pool
+// and must not grow the process footprint behind that pool's back. The plan-based entry
+// points above allocate their cross-slice scratch with cudaMallocAsync when the plan is
+// created; the entry point below needs no plan and no allocation. Its scratch lives in the two
+// file-scope device arrays that follow, which every GPU that loads this library holds until
+// the process exits (1 MiB + 4 KiB per device).
+namespace mircuda_b200 {
+namespace fp4_vector {
+
+constexpr size_t kStaticPartialFloats = 262144;   // slices * padded rows must fit: 1 MiB
+constexpr size_t kStaticRowTiles = 1024;          // N <= 131072
+
+static __device__ __align__(256) float static_partials[kStaticPartialFloats];
+static __device__ __align__(256) unsigned int static_counters[kStaticRowTiles];
+
+struct StaticScratch {
+  float* partials;
+  unsigned int* counters;
+  bool ready;
+};
+
+// In host code the array names above are host-side stand-ins, not device addresses; the
+// device addresses are looked up once per device, with that device current, and cached.
+int static_scratch(StaticScratch** result) {
+  constexpr int kMaxDevices = 64;
+  static StaticScratch cache[kMaxDevices] = {};
+  static std::mutex guard;
+  int device = 0;
+  int status = static_cast<int>(cudaGetDevice(&device));
+  if (status != 0) return status;
+  if (device < 0 || device >= kMaxDevices) return -1;
+  std::lock_guard<std::mutex> lock(guard);
+  StaticScratch& entry = cache[device];
+  if (!entry.ready) {
+    void* partials = nullptr;
+    void* counters = nullptr;
+    status = static_cast<int>(cudaGetSymbolAddress(&partials, static_partials));
+    if (status != 0) return status;
+    status = static_cast<int>(cudaGetSymbolAddress(&counters, static_counters));
+    if (status != 0) return status;
+    entry.partials = static_cast<float*>(partials);
+    entry.counters = static_cast<unsigned int*>(counters);
+    entry.ready = true;
+  }
+  *result = &entry;
+  return 0;
+}
+
+}  // namespace fp4_vector
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_fp4_vector_execute_static(int n, int k, void* stream,
+                                                      const void* input,
+                                                      const void* input_scales,
+                                                      const void* weight,
+                                                      const void* weight_scales, void* output,
+                                                      float alpha) {
+  using namespace mircuda_b200::fp4_vector;
+  if (n <= 0 || k <= 0 || k % 64 != 0 || stream == nullptr || input == nullptr ||
+      input_scales == nullptr || weight == nullptr || weight_scales == nullptr ||
+      output == nullptr) {
+    return -1;
+  }
+  if (((reinterpret_cast<uintptr_t>(input) | reinterpret_cast<uintptr_t>(weight) |
+        reinterpret_cast<uintptr_t>(weight_scales)) & 15u) != 0u) {
+    return -1;
+  }
+  const size_t slices = (static_cast<size_t>(k) + kTileK - 1) / kTileK;
+  const size_t row_tiles = (static_cast<size_t>(n) + kTileRows - 1) / kTileRows;
+  if (row_tiles > kStaticRowTiles || slices * row_tiles * kTileRows > kStaticPartialFloats) {
+    return -4;  // the shape needs more scratch than the static arrays hold
+  }
+  StaticScratch* scratch = nullptr;
+  int status = static_scratch(&scratch);
+  if (status != 0) return status;
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  if (slices > 1) {
+    // The arrays keep whatever the previous call left; the arrival counters must start at 0.
+    status = static_cast<int>(cudaMemsetAsync(scratch->counters, 0,
+                                              row_tiles * sizeof(unsigned int), cuda_stream));
+    if (status != 0) return status;
+  }
+  const dim3 grid(static_cast<unsigned int>(row_tiles), static_cast<unsigned int>(slices));
+  fp4_vector_kernel<<<grid, kThreads, 0, cuda_stream>>>(
+      static_cast<const uint8_t*>(input), static_cast<const uint8_t*>(input_scales),
+      static_cast<const uint8_t*>(weight), static_cast<const uint8_t*>(weight_scales),
+      static_cast<__nv_bfloat16*>(output), scratch->partials, scratch->counters, n, k,
+      static_cast<int>(slices), alpha);
+  return static_cast<int>(cudaPeekAtLastError());
 }
