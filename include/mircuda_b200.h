@@ -121,6 +121,19 @@ int mircuda_b200_nvfp4_global_scale(const void* input, size_t elements, void* gl
 int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale, void* codes,
                                      void* scales, uint32_t rows, uint32_t k, void* stream);
 
+/* -------------------------------------------------- variable-row grouped bf16 GEMM ----
+ * For each group g: C[off_g : off_g + min(rows_g, max_rows), :] = A[same rows] . W_g^T
+ * (+ beta C); A [capacity, k], W [groups, n, k], C [capacity, n], all bf16; rows/offsets
+ * are device u32 arrays that the host never reads. n % 8 == 0, k % 8 == 0.
+ * Replaces sys/native/variable_grouped_bf16_sm120.cu:147-185, declared in
+ * sys/src/platform/cutlass/variable_grouped/bf16.rs:11-31. */
+int mircuda_variable_grouped_bf16_create(int groups, int max_rows, int n, int k, void* stream,
+                                         void** output);
+int mircuda_variable_grouped_bf16_execute(void* plan, void* stream, const void* input,
+                                          const void* weights, const unsigned int* rows,
+                                          const unsigned int* offsets, void* output, float beta);
+void mircuda_variable_grouped_bf16_destroy(void* plan);
+
 #ifdef __cplusplus
 }
 #endif

@@ -39,6 +39,9 @@ SIGNATURES = {
     "mircuda_b200_nvfp4_vector_destroy": (None, [_vp]),
     "mircuda_b200_nvfp4_global_scale": (_i, [_vp, _sz, _vp, _vp]),
     "mircuda_b200_nvfp4_quantize_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
+    "mircuda_variable_grouped_bf16_create": (_i, [_i, _i, _i, _i, _vp, _vpp]),
+    "mircuda_variable_grouped_bf16_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
+    "mircuda_variable_grouped_bf16_destroy": (None, [_vp]),
 }
 
 _handle = None

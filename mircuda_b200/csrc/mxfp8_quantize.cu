@@ -39,9 +39,21 @@ __device__ __forceinline__ float inverse_scale(uint32_t exponent_byte) {
   return __uint_as_float(bits);
 }
 
-__device__ __forceinline__ uint32_t magnitude_for_max(uint32_t half_bits) {
-  const uint32_t magnitude = half_bits & 0x7fffu;
-  return magnitude > 0x7f80u ? 0u : magnitude;  // NaN takes no part, as with fmaxf
+// Largest magnitude of the eight bf16 values of a 16-byte vector, as bf16x2 (each half holds
+// the maximum of its four lanes). Packed max ignores a NaN operand, as fmaxf does.
+__device__ __forceinline__ uint32_t packed_abs_max(const uint4& v) {
+  const __nv_bfloat162 a = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v.x));
+  const __nv_bfloat162 b = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v.y));
+  const __nv_bfloat162 c = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v.z));
+  const __nv_bfloat162 d = __habs2(*reinterpret_cast<const __nv_bfloat162*>(&v.w));
+  const __nv_bfloat162 m = __hmax2(__hmax2(a, b), __hmax2(c, d));
+  return *reinterpret_cast<const uint32_t*>(&m);
+}
+
+__device__ __forceinline__ uint32_t packed_max(uint32_t a, uint32_t b) {
+  const __nv_bfloat162 m = __hmax2(*reinterpret_cast<const __nv_bfloat162*>(&a),
+                                   *reinterpret_cast<const __nv_bfloat162*>(&b));
+  return *reinterpret_cast<const uint32_t*>(&m);
 }
 
 // Two bf16 (packed in a u32, low half first) times `inverse` -> two E4M3 codes (low byte first).
@@ -52,33 +64,39 @@ __device__ __forceinline__ uint32_t encode_pair(uint32_t packed, float inverse) 
       __nv_cvt_float2_to_fp8x2(make_float2(low, high), __NV_SATFINITE, __NV_E4M3));
 }
 
+// group / groups_per_row by multiply-and-shift (group < 2^31): quotient = group * magic >> shift.
+struct Divisor {
+  uint32_t divisor;
+  uint32_t magic;
+  uint32_t shift;
+};
+
+__device__ __forceinline__ uint32_t divide(uint32_t value, const Divisor& d) {
+  return static_cast<uint32_t>((static_cast<uint64_t>(value) * d.magic) >> d.shift);
+}
+
 template <bool kPackedScales>
 __global__ void __launch_bounds__(kThreads)
 mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
-                uint8_t* __restrict__ scales, uint32_t rows, uint32_t columns) {
-  const uint32_t vectors_per_row = columns / 8u;
-  const uint32_t groups_per_row = columns / 32u;
-  const uint64_t vectors = static_cast<uint64_t>(rows) * vectors_per_row;
-  const uint64_t first =
-      static_cast<uint64_t>(blockIdx.x) * (kThreads * kVectorsPerThread) + threadIdx.x;
+                      uint8_t* __restrict__ scales, uint32_t vectors, Divisor groups_per_row) {
+  const uint32_t first = blockIdx.x * (kThreads * kVectorsPerThread) + threadIdx.x;
 
   uint4 values[kVectorsPerThread];
 #pragma unroll
   for (int item = 0; item < kVectorsPerThread; ++item) {
-    const uint64_t vector = first + static_cast<uint64_t>(item) * kThreads;
+    const uint32_t vector = first + item * kThreads;
     values[item] = vector < vectors ? __ldg(input + vector) : make_uint4(0u, 0u, 0u, 0u);
   }
 
 #pragma unroll
   for (int item = 0; item < kVectorsPerThread; ++item) {
-    const uint64_t vector = first + static_cast<uint64_t>(item) * kThreads;
+    const uint32_t vector = first + item * kThreads;
     const uint4 v = values[item];
-    uint32_t maximum = max(max(magnitude_for_max(v.x), magnitude_for_max(v.x >> 16)),
-                           max(magnitude_for_max(v.y), magnitude_for_max(v.y >> 16)));
-    maximum = max(maximum, max(max(magnitude_for_max(v.z), magnitude_for_max(v.z >> 16)),
-                               max(magnitude_for_max(v.w), magnitude_for_max(v.w >> 16))));
-    maximum = max(maximum, __shfl_xor_sync(0xffffffffu, maximum, 1));
-    maximum = max(maximum, __shfl_xor_sync(0xffffffffu, maximum, 2));
+    uint32_t both = packed_abs_max(v);
+    both = packed_max(both, __shfl_xor_sync(0xffffffffu, both, 1));
+    both = packed_max(both, __shfl_xor_sync(0xffffffffu, both, 2));
+    uint32_t maximum = max(both & 0xffffu, both >> 16);
+    if (maximum > 0x7f80u) maximum = 0u;  // only when every element of the block is NaN
     const uint32_t exponent = scale_exponent(maximum);
     const float inverse = inverse_scale(exponent);
     const uint32_t low = encode_pair(v.x, inverse) | (encode_pair(v.y, inverse) << 16);
@@ -88,9 +106,6 @@ mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ outpu
     // One scale byte per 4-thread group. A warp holds 8 consecutive groups; when rows are a
     // multiple of 128 columns those are two aligned quartets whose bytes are adjacent in the
     // swizzled atom, so lanes 0 and 16 each write one 32-bit word.
-    const uint64_t group = vector / 4u;
-    const uint32_t row = static_cast<uint32_t>(group / groups_per_row);
-    const uint32_t group_in_row = static_cast<uint32_t>(group % groups_per_row);
     if constexpr (kPackedScales) {
       const uint32_t lane = threadIdx.x & 31u;
       const uint32_t base = lane & 16u;
@@ -99,12 +114,19 @@ mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ outpu
                             (__shfl_sync(0xffffffffu, exponent, base + 8u) << 16) |
                             (__shfl_sync(0xffffffffu, exponent, base + 12u) << 24);
       if ((lane & 15u) == 0u && vector < vectors) {
-        *reinterpret_cast<uint32_t*>(scales + scale_offset(row, group_in_row, groups_per_row)) =
-            word;
+        const uint32_t group = vector / 4u;
+        const uint32_t row = divide(group, groups_per_row);
+        const uint32_t group_in_row = group - row * groups_per_row.divisor;
+        *reinterpret_cast<uint32_t*>(
+            scales + scale_offset(row, group_in_row, groups_per_row.divisor)) = word;
       }
     } else {
       if ((threadIdx.x & 3u) == 0u && vector < vectors) {
-        scales[scale_offset(row, group_in_row, groups_per_row)] = static_cast<uint8_t>(exponent);
+        const uint32_t group = vector / 4u;
+        const uint32_t row = divide(group, groups_per_row);
+        const uint32_t group_in_row = group - row * groups_per_row.divisor;
+        scales[scale_offset(row, group_in_row, groups_per_row.divisor)] =
+            static_cast<uint8_t>(exponent);
       }
     }
   }
@@ -136,18 +158,26 @@ extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output,
     return -1;
   }
   const uint64_t vectors = static_cast<uint64_t>(rows) * (columns / 8u);
+  if (vectors >= (1ull << 32)) return -1;  // group indices are 32-bit inside the kernel
   const uint64_t per_block = kThreads * kVectorsPerThread;
   const uint64_t blocks = (vectors + per_block - 1u) / per_block;
-  if (blocks > 0x7fffffffull) return -1;
+  // Exact multiply-and-shift division for dividends below 2^31: with s = ceil(log2(d)) and
+  // magic = ceil(2^(31+s) / d) < 2^32, floor(n / d) == (n * magic) >> (31 + s).
+  Divisor divisor{columns / 32u, 0u, 0u};
+  uint32_t log2_ceiling = 0;
+  while ((1ull << log2_ceiling) < divisor.divisor) ++log2_ceiling;
+  divisor.shift = 31u + log2_ceiling;
+  divisor.magic = static_cast<uint32_t>(((1ull << divisor.shift) + divisor.divisor - 1u) /
+                                        divisor.divisor);
   auto cuda_stream = static_cast<cudaStream_t>(stream);
   if (columns % 128u == 0u) {
     mxfp8_quantize_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
         static_cast<const uint4*>(input), static_cast<uint2*>(output),
-        static_cast<uint8_t*>(scales), rows, columns);
+        static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor);
   } else {
     mxfp8_quantize_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
         static_cast<const uint4*>(input), static_cast<uint2*>(output),
-        static_cast<uint8_t*>(scales), rows, columns);
+        static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor);
   }
   return static_cast<int>(cudaPeekAtLastError());
 }

@@ -408,3 +408,57 @@ def nvfp4_quantize_bf16(stream, values: torch.Tensor):
         _device_pointer(values, _BF16), ctypes.c_void_p(global_scale.data_ptr()),
         _device_pointer(codes, _BYTES), _device_pointer(scales, _BYTES), rows, k, handle))
     return codes.view(rows, k // 2), scales, global_scale
+
+
+# --------------------------------------------------------------------------- grouped MoE
+
+@dataclass(frozen=True)
+class VariableGroupedBf16Spec:
+    """``VariableGroupedBf16Spec`` (src/cutlass/variable_grouped/bf16.rs:4-81)."""
+    groups: int
+    max_rows: int
+    n: int
+    k: int
+    capacity_rows: int
+
+    def __post_init__(self):
+        values = (self.groups, self.max_rows, self.n, self.k, self.capacity_rows)
+        if any(v <= 0 for v in values) or self.n % 8 != 0 or self.k % 8 != 0:
+            raise InvalidMatmulShape("invalid grouped bf16 shape")
+        if max(values) > 2**32 - 1:
+            raise InvalidMatmulShape("dimension does not fit u32")
+
+
+class VariableGroupedBf16Plan:
+    """``VariableGroupedBf16Plan`` (src/cutlass/variable_grouped/bf16.rs:83-124): all products
+    are enqueued without the host ever reading ``rows`` / ``offsets``."""
+
+    def __init__(self, stream, spec: VariableGroupedBf16Spec):
+        self._lib = _lib.load()
+        self.spec, self._stream = spec, stream
+        raw = ctypes.c_void_p()
+        _check(self._lib.mircuda_variable_grouped_bf16_create(
+            spec.groups, spec.max_rows, spec.n, spec.k, _stream_handle(stream), ctypes.byref(raw)))
+        self._raw = raw
+
+    def execute(self, stream, input, weights, rows, offsets, output, beta: float = 0.0):
+        if stream.cuda_stream != self._stream.cuda_stream:
+            raise StreamMismatch()
+        s = self.spec
+        _exact("input", s.capacity_rows * s.k, input)
+        _exact("weights", s.groups * s.n * s.k, weights)
+        _exact("rows", s.groups, rows)
+        _exact("offsets", s.groups, offsets)
+        _exact("output", s.capacity_rows * s.n, output)
+        words = (torch.int32, torch.uint32)
+        _check(self._lib.mircuda_variable_grouped_bf16_execute(
+            self._raw, _stream_handle(stream), _device_pointer(input, _BF16),
+            _device_pointer(weights, _BF16), _device_pointer(rows, words),
+            _device_pointer(offsets, words), _device_pointer(output, _BF16), float(beta)))
+
+    def close(self):
+        if getattr(self, "_raw", None):
+            self._lib.mircuda_variable_grouped_bf16_destroy(self._raw)
+            self._raw = None
+
+    __del__ = close
