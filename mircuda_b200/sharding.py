@@ -27,9 +27,9 @@ def column_shard(n: int, world: int, rank: int, granule: int = 128) -> tuple[int
 def gather_columns(shards, out=None, group=None):
     """All-gather per-rank outputs [M, N_r] into the full [M, N] (columns in rank order).
 
-    `shards` is this rank's [M, N_r] tensor. Equal shard widths use one
-    all_gather_into_tensor; unequal widths fall back to all_gather of a list. Works with any
-    torch.distributed backend (nccl on GPUs, gloo in the CPU tests).
+    `shards` is this rank's [M, N_r] tensor. Narrower shards are zero-padded to the widest
+    one for the collective and cut back afterwards. Works with any torch.distributed
+    backend (nccl on GPUs, gloo in the CPU tests).
     """
     import torch
     import torch.distributed as dist
@@ -39,9 +39,14 @@ def gather_columns(shards, out=None, group=None):
     widths = [torch.zeros(1, dtype=torch.int64, device=shards.device) for _ in range(world)]
     dist.all_gather(widths, torch.tensor([local_n], dtype=torch.int64, device=shards.device), group=group)
     widths = [int(w.item()) for w in widths]
-    pieces = [torch.empty(m, w, dtype=shards.dtype, device=shards.device) for w in widths]
-    dist.all_gather(pieces, shards.contiguous(), group=group)
-    full = torch.cat(pieces, dim=1)
+    widest = max(widths)
+    padded = shards.contiguous()
+    if local_n != widest:                      # collectives want equal sizes on every rank
+        padded = torch.zeros(m, widest, dtype=shards.dtype, device=shards.device)
+        padded[:, :local_n] = shards
+    pieces = [torch.empty(m, widest, dtype=shards.dtype, device=shards.device) for _ in widths]
+    dist.all_gather(pieces, padded, group=group)
+    full = torch.cat([piece[:, :width] for piece, width in zip(pieces, widths)], dim=1)
     if out is not None:
         out.copy_(full)
         return out
