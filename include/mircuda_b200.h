@@ -65,6 +65,17 @@ int mircuda_b200_mxfp8_bf16(const void* input, const void* weight, const void* s
                             void* output, uint32_t tokens, uint32_t input_features,
                             uint32_t output_features, void* stream);
 
+/* ---------------------------------------------------------- NVFP4 block-scaled GEMM ----
+ * C[m,n] (bf16) = alpha * A[m,k] (E2M1) . B[n,k]^T (E2M1), one UE4M3 scale per 16 K-elements
+ * of each operand in the swizzled layout, fp32 accumulation. k % 64 == 0.
+ * Replaces sys/native/fp4_sm120.cu:110-170, declared in
+ * sys/src/platform/cutlass/fp4/mod.rs:15-35. */
+int mircuda_fp4_create(int m, int n, int k, void* stream, void** output);
+size_t mircuda_fp4_workspace_bytes(const void* plan);
+int mircuda_fp4_execute(void* plan, void* stream, const void* a, const void* a_scales,
+                        const void* b, const void* b_scales, void* c, float alpha);
+void mircuda_fp4_destroy(void* plan);
+
 /* ----------------------------------------------------------- FP4 x FP4 GEMV (M = 1) ----
  * y[n] (bf16) = alpha * sum_k e2m1(x) e2m1(W) sx sw; k % 64 == 0.
  * Replaces sys/native/fp4_vector_sm120.cu:127-168, declared in

@@ -27,6 +27,10 @@ SIGNATURES = {
     "mircuda_mxfp8_tc_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mircuda_mxfp8_tc_destroy": (None, [_vp]),
     "mircuda_b200_mxfp8_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mircuda_fp4_create": (_i, [_i, _i, _i, _vp, _vpp]),
+    "mircuda_fp4_workspace_bytes": (_sz, [_vp]),
+    "mircuda_fp4_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
+    "mircuda_fp4_destroy": (None, [_vp]),
     "mircuda_fp4_vector_create": (_i, [_i, _i, _vp, _vpp]),
     "mircuda_fp4_vector_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _f]),
     "mircuda_fp4_vector_destroy": (None, [_vp]),

@@ -332,6 +332,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
   ptx::tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     ptx::tcgen05_fence_after();
     ptx::tmem_deallocate(tmem_base, kTmemColumns);
   }

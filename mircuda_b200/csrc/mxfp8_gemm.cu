@@ -23,6 +23,7 @@
 #include <cstdlib>
 #include <new>
 
+#include "block_scaled_pair_gemm.cuh"
 #include "layout.cuh"
 #include "ptx.cuh"
 #include "tensor_map.hpp"
@@ -268,6 +269,7 @@ mxfp8_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   ptx::tcgen05_fence_before();
   __syncthreads();
   if (warp == 1) {
+    __syncwarp();
     ptx::tcgen05_fence_after();
     ptx::tmem_deallocate(tmem_base, kTmemColumns);
   }
@@ -286,6 +288,11 @@ struct Plan {
   const void* cached_a;
   const void* cached_b;
   CUtensorMap map_a, map_b;
+  // CTA-pair kernel (used when M > 128): four tensor maps that depend on all four operands.
+  bool pair;
+  const void* cached_a_scales;
+  const void* cached_b_scales;
+  pair_gemm::Maps pair_maps;
 };
 
 template <uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
@@ -336,6 +343,64 @@ uint32_t choose_block_n(int m, int n, int k, int sm_count) {
   return best;
 }
 
+// Tile width for the CTA-pair kernel (256-row tiles on sm_count / 2 pairs): whole waves of
+// work times a per-width cost. 256 columns leave room for one accumulator stage only, so the
+// epilogue of a tile is exposed; 192 columns double-buffer the accumulator but move more
+// shared-memory bytes per MMA cycle. (Widths that are not a multiple of 64 would make a tile
+// start an odd number of columns into its scale block in tensor memory, which the MMA rejects
+// as a misaligned address.)
+uint32_t choose_pair_block_n(int m, int n, int k, int sm_count) {
+  if (const char* forced = std::getenv("MIRCUDA_B200_GEMM_BN")) {
+    const int value = std::atoi(forced);
+    if (value == 128 || value == 192 || value == 256) return static_cast<uint32_t>(value);
+  }
+  const uint32_t candidates[3] = {256u, 192u, 128u};
+  const double k_stages = static_cast<double>(k) / 128.0;
+  // Measured on the prefill shapes: the 192-wide tile (two accumulator stages) beats the
+  // 256-wide one (one stage, exposed epilogue) by 10-20 % at equal wave counts.
+  const double penalty[3] = {1.12 + 2.0 / (k_stages + 1.0), 1.0, 1.30};
+  const int pairs = sm_count / 2 > 0 ? sm_count / 2 : 1;
+  uint32_t best = 256u;
+  double best_cost = 0.0;
+  for (int index = 0; index < 3; ++index) {
+    const uint32_t bn = candidates[index];
+    const uint64_t tiles = static_cast<uint64_t>((m + 255) / 256) * ((n + bn - 1u) / bn);
+    const uint64_t waves = (tiles + pairs - 1) / pairs;
+    const double cost = static_cast<double>(waves) * bn * penalty[index];
+    if (index == 0 || cost < best_cost) {
+      best = bn;
+      best_cost = cost;
+    }
+  }
+  return best;
+}
+
+int execute_pair(Plan* plan, const void* a, const void* a_scales, const void* b,
+                 const void* b_scales, void* c) {
+  using pair_gemm::Format;
+  pair_gemm::Problem problem{static_cast<uint32_t>(plan->m), static_cast<uint32_t>(plan->n),
+                             static_cast<uint32_t>(plan->k), plan->device, plan->sm_count,
+                             plan->stream, plan->status};
+  if (a != plan->cached_a || b != plan->cached_b || a_scales != plan->cached_a_scales ||
+      b_scales != plan->cached_b_scales) {
+    const int status = pair_gemm::encode_maps<Format::kMxFp8>(&plan->pair_maps, problem,
+                                                              plan->block_n, a, a_scales, b, b_scales);
+    if (status != 0) return status;
+    plan->cached_a = a;
+    plan->cached_b = b;
+    plan->cached_a_scales = a_scales;
+    plan->cached_b_scales = b_scales;
+  }
+  switch (plan->block_n) {
+    case 128u:
+      return pair_gemm::launch<Format::kMxFp8, 128u, 8u, 2u>(problem, plan->pair_maps, c, 1.0f);
+    case 192u:
+      return pair_gemm::launch<Format::kMxFp8, 192u, 7u, 2u>(problem, plan->pair_maps, c, 1.0f);
+    default:
+      return pair_gemm::launch<Format::kMxFp8, 256u, 6u, 1u>(problem, plan->pair_maps, c, 1.0f);
+  }
+}
+
 }  // namespace mxfp8_gemm
 }  // namespace mircuda_b200
 
@@ -364,7 +429,10 @@ extern "C" int mircuda_mxfp8_tc_create(int m, int n, int k, void* stream, void**
     return status;
   }
   *plan->status = 0u;
-  plan->block_n = choose_block_n(m, n, k, plan->sm_count);
+  const char* mode = std::getenv("MIRCUDA_B200_GEMM_PAIR");   // "0" forces the unpaired kernel
+  plan->pair = m > 128 && plan->sm_count >= 2 && !(mode != nullptr && mode[0] == '0');
+  plan->block_n = plan->pair ? choose_pair_block_n(m, n, k, plan->sm_count)
+                             : choose_block_n(m, n, k, plan->sm_count);
   *output = plan;
   return 0;
 }
@@ -391,6 +459,7 @@ extern "C" int mircuda_mxfp8_tc_execute(void* raw, void* stream, const void* a,
         reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u) != 0u) {
     return -1;
   }
+  if (plan->pair) return execute_pair(plan, a, a_scales, b, b_scales, c);
   if (a != plan->cached_a) {
     const int status = encode_k_major_map(&plan->map_a, a, plan->m, plan->k, 1u, kBlockM);
     if (status != 0) return status;
