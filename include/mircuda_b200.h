@@ -19,6 +19,7 @@
 #ifndef MIRCUDA_B200_H
 #define MIRCUDA_B200_H
 
+#include <stdbool.h>
 #include <stddef.h>
 #include <stdint.h>
 
@@ -144,6 +145,30 @@ int mircuda_variable_grouped_bf16_execute(void* plan, void* stream, const void* 
                                           const void* weights, const unsigned int* rows,
                                           const unsigned int* offsets, void* output, float beta);
 void mircuda_variable_grouped_bf16_destroy(void* plan);
+
+/* ------------------------------------------------- Marlin-layout W4A16: preparation ----
+ * One-time layout conversions and per-step route bucketing; stateless, integer, bit-exact.
+ * Replace sys/native/marlin/repack.cu:271-end, declared in
+ * sys/src/platform/marlin/prepare/mod.rs:12-42, prepare/mxfp4.rs and execute/mod.rs:18-31.
+ * size_n % 64 == 0, size_k % 16 == 0 (32 for MXFP4 scales). `maximum` is a caller-owned
+ * device u32 scratch; `sorted` holds assignments + experts * (block_size - 1) entries. */
+int mircuda_marlin_nvfp4_repack(void* stream, const void* input, void* output, int experts,
+                                int size_n, int size_k);
+int mircuda_marlin_nvfp4_repack_pair(void* stream, const void* left, const void* right,
+                                     void* output, int experts, int size_n, int size_k);
+int mircuda_marlin_mxfp4_repack(void* stream, const void* input, void* output, int experts,
+                                int size_n, int size_k, int logical_n, int logical_k,
+                                bool interleaved_gate_up);
+int mircuda_marlin_mxfp4_prepare_scales(void* stream, const void* input, void* output,
+                                        int experts, int size_n, int size_k, int logical_n,
+                                        int logical_k, bool interleaved_gate_up);
+int mircuda_marlin_nvfp4_prepare_scales(void* stream, const void* left, const void* right,
+                                        const void* globals, void* output, void* output_globals,
+                                        void* maximum, int experts, int size_n, int size_k);
+int mircuda_marlin_prepare_moe_routes(void* stream, const void* selected, const void* routing,
+                                      void* sorted, void* expert_ids, void* padded, void* offsets,
+                                      void* routing_f32, int assignments, int experts,
+                                      int block_size);
 
 #ifdef __cplusplus
 }

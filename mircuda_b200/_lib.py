@@ -48,6 +48,16 @@ SIGNATURES = {
     "mircuda_variable_grouped_bf16_destroy": (None, [_vp]),
 }
 
+_b = ctypes.c_bool
+SIGNATURES.update({
+    "mircuda_marlin_nvfp4_repack": (_i, [_vp, _vp, _vp, _i, _i, _i]),
+    "mircuda_marlin_nvfp4_repack_pair": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mircuda_marlin_mxfp4_repack": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _b]),
+    "mircuda_marlin_mxfp4_prepare_scales": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _b]),
+    "mircuda_marlin_nvfp4_prepare_scales": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
+    "mircuda_marlin_prepare_moe_routes": (_i, [_vp] * 8 + [_i, _i, _i]),
+})
+
 _handle = None
 
 

@@ -57,4 +57,12 @@ __device__ __forceinline__ float decode_ue4m3(uint8_t code) {
   return __half2float(__ushort_as_half(static_cast<unsigned short>(pair & 0xffffu)));
 }
 
+// Full E4M3 decode (sign kept, 0x7f / 0xff are NaN), through the same conversion.
+__device__ __forceinline__ float decode_e4m3_signed(uint8_t code) {
+  uint32_t pair;
+  const uint16_t source = static_cast<uint16_t>(code);
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(source));
+  return __half2float(__ushort_as_half(static_cast<unsigned short>(pair & 0xffffu)));
+}
+
 }  // namespace mircuda_b200
