@@ -170,6 +170,20 @@ int mircuda_marlin_prepare_moe_routes(void* stream, const void* selected, const 
                                       void* routing_f32, int assignments, int experts,
                                       int block_size);
 
+/* --------------------------------------------------- Marlin-layout W4A16: execution ----
+ * bf16 activations [tokens <= 16, k] x NVFP4 weights in Marlin tiles (prepared above) ->
+ * bf16 [tokens, n]; fp32 accumulation, prepared global scale applied before the bf16 round.
+ * `temporary` (>= SMs * 4096 floats) and `locks` (>= SMs ints, zero on entry, left zero)
+ * are the caller-owned reduction workspace of the reference interface; `thread_config` and
+ * `atomic_reduce` are accepted and ignored (one tile geometry, ordered reduction).
+ * Replaces sys/native/marlin/dense_kernel.cu:73-102, declared in
+ * sys/src/platform/marlin/execute/dense.rs:16-31. n % 64 == 0, k % 16 == 0. */
+int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* input, const void* weight,
+                                       void* output, void* temporary, const void* scales,
+                                       const float* global_scale, int tokens,
+                                       int output_features, int input_features,
+                                       int thread_config, void* locks, bool atomic_reduce);
+
 #ifdef __cplusplus
 }
 #endif

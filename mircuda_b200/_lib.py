@@ -56,6 +56,7 @@ SIGNATURES.update({
     "mircuda_marlin_mxfp4_prepare_scales": (_i, [_vp, _vp, _vp, _i, _i, _i, _i, _i, _b]),
     "mircuda_marlin_nvfp4_prepare_scales": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i]),
     "mircuda_marlin_prepare_moe_routes": (_i, [_vp] * 8 + [_i, _i, _i]),
+    "mircuda_marlin_nvfp4_dense_execute": (_i, [_vp] * 7 + [_i, _i, _i, _i, _vp, _b]),
 })
 
 _handle = None

@@ -1,0 +1,174 @@
+"""Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
+
+    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin]
+
+Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
+examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
+banks that their total exceeds 768 MiB (at least 8 banks), so no launch finds its matrix in
+the 126 MB L2; `cycles` back-to-back launches are timed between two CUDA events on the
+launching stream after a warm-up pass; the median of `repeats` timings is reported.
+Bytes counted per launch are the algorithmic ones: weights + scales + activations + outputs.
+Shapes: the four Qwen3-8B linears (N, K) at M in {1, 4, 8}. Prints one JSON line per op and
+a final summary line.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import math
+import statistics
+
+import torch
+
+from . import _lib, plans
+
+SHAPES = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288)]
+BANK_BYTES = 768 << 20
+
+
+def _banks(bytes_per_bank: int) -> int:
+    return max(8, math.ceil(BANK_BYTES / bytes_per_bank))
+
+
+def _time(stream, launch, banks: int, cycles: int, repeats: int) -> float:
+    """Median seconds per launch."""
+    for index in range(banks):
+        launch(index)
+    stream.synchronize()
+    # The launches are microseconds long: issue them from a CUDA graph (as the reference's
+    # callers do, examples/graph.rs) so that host launch cost is not what gets measured.
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=stream):
+        for cycle in range(cycles):
+            launch(cycle % banks)
+    graph.replay()
+    torch.cuda.synchronize()
+    samples = []
+    for _ in range(repeats):
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        graph.replay()
+        stop.record()
+        torch.cuda.synchronize()
+        samples.append(start.elapsed_time(stop) * 1e-3 / cycles)
+    return statistics.median(samples)
+
+
+def _random_bytes(count: int, low: int, high: int) -> torch.Tensor:
+    return torch.randint(low, high, (count,), dtype=torch.uint8, device="cuda")
+
+
+def bench_nvfp4(stream, n, k, m, cycles, repeats):
+    scale_bytes = (n + 127) // 128 * (k // 64) * 512
+    banks = _banks(n * k // 2 + scale_bytes)
+    weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+    scales = [_random_bytes(scale_bytes, 0x28, 0x48) for _ in range(banks)]
+    x = torch.randn(m * k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    plan = plans.NvFp4VectorPlan(stream, plans.NvFp4VectorSpec(m, n, k))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute(stream, x, weights[i], scales[i], out, 0.5),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, n * k * 0.5625 + m * k * 2 + m * n * 2, banks
+
+
+def bench_fp4(stream, n, k, cycles, repeats):
+    scale_bytes = (n + 127) // 128 * (k // 64) * 512
+    banks = _banks(n * k // 2 + scale_bytes)
+    weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+    scales = [_random_bytes(scale_bytes, 0x28, 0x48) for _ in range(banks)]
+    x = _random_bytes(k // 2, 0, 256)
+    xs = _random_bytes((k // 64) * 512, 0x28, 0x48)
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    plan = plans.BlockScaledFp4VectorPlan(stream, plans.BlockScaledFp4VectorSpec(n, k))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute(stream, x, xs, weights[i], scales[i], out, 0.5),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, n * k * 0.5625 + k * 0.5625 + n * 2, banks
+
+
+def bench_dense(stream, n, k, cycles, repeats):
+    banks = _banks(n * k * 2)
+    weights = [(torch.randn(n * k, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(banks)]
+    x = torch.randn(k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+    plan = plans.DenseVectorPlan(stream, plans.DenseVectorSpec(n, k, 1))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute(stream, x, weights[i], out, 1.0, 0.0),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, 2.0 * n * k + 2 * k + 2 * n, banks
+
+
+def bench_marlin(stream, n, k, m, cycles, repeats):
+    library = _lib.load()
+    banks = _banks(n * k // 2 + n * k // 16)
+    weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+    scales = [_random_bytes(n * k // 16, 0x90, 0xF0) for _ in range(banks)]   # prepared codes
+    x = torch.randn(m * k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    sms = torch.cuda.get_device_properties(0).multi_processor_count
+    temporary = torch.zeros(sms * 4096, dtype=torch.float32, device="cuda")
+    locks = torch.zeros(sms, dtype=torch.int32, device="cuda")
+    global_scale = torch.full((1,), 2.0 ** 100, dtype=torch.float32, device="cuda")
+    handle = ctypes.c_void_p(stream.cuda_stream)
+    torch.cuda.synchronize()
+
+    def launch(index):
+        status = library.mircuda_marlin_nvfp4_dense_execute(
+            handle, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(weights[index].data_ptr()),
+            ctypes.c_void_p(out.data_ptr()), ctypes.c_void_p(temporary.data_ptr()),
+            ctypes.c_void_p(scales[index].data_ptr()), ctypes.c_void_p(global_scale.data_ptr()),
+            m, n, k, 0, ctypes.c_void_p(locks.data_ptr()), False)
+        if status != 0:
+            raise RuntimeError(f"marlin dense status {status}")
+
+    seconds = _time(stream, launch, banks, cycles, repeats)
+    return seconds, n * k * 0.5625 + m * k * 2 + m * n * 2, banks
+
+
+def run(ops, cycles: int, repeats: int, peak_gbs: float) -> dict:
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    results = []
+    for op in ops:
+        for name, n, k in SHAPES:
+            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1]):
+                with torch.cuda.stream(stream):
+                    if op == "nvfp4":
+                        seconds, byte_count, banks = bench_nvfp4(stream, n, k, m, cycles, repeats)
+                    elif op == "fp4":
+                        seconds, byte_count, banks = bench_fp4(stream, n, k, cycles, repeats)
+                    elif op == "dense":
+                        seconds, byte_count, banks = bench_dense(stream, n, k, cycles, repeats)
+                    else:
+                        seconds, byte_count, banks = bench_marlin(stream, n, k, m, cycles, repeats)
+                torch.cuda.empty_cache()
+                record = {"op": op, "shape": name, "n": n, "k": k, "m": m, "us": seconds * 1e6,
+                          "gbs": byte_count / seconds / 1e9, "frac_of_measured_hbm":
+                          byte_count / seconds / 1e9 / peak_gbs, "banks": banks}
+                results.append(record)
+                print(json.dumps(record), flush=True)
+    return {"results": results}
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--cycles", type=int, default=200)
+    parser.add_argument("--repeats", type=int, default=5)
+    parser.add_argument("--ops", default="nvfp4,fp4,dense,marlin")
+    parser.add_argument("--peak-gbs", type=float, default=6551.4)
+    args = parser.parse_args()
+    summary = run(args.ops.split(","), args.cycles, args.repeats, args.peak_gbs)
+    by_op = {}
+    for record in summary["results"]:
+        by_op.setdefault(record["op"], []).append(record["frac_of_measured_hbm"])
+    print(json.dumps({"summary": {op: {"min_frac": min(v), "mean_frac": sum(v) / len(v)}
+                                  for op, v in by_op.items()}}), flush=True)
+
+
+if __name__ == "__main__":
+    main()

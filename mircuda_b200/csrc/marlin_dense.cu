@@ -1,0 +1,294 @@
+// W4A16 dense projection on the Marlin layout for decode: bf16 activations [tokens <= 16, K]
+// times NVFP4 weights that were repacked into Marlin tiles (marlin_prepare.cu) with their
+// group-16 scales prepared into the permuted 8-bit form, to bf16 [tokens, N]. Replaces the
+// reference's vendored Marlin kernel instantiation (sys/native/marlin/dense_kernel.cu:73-102)
+// behind the same C entry point. Numerics: exact weight * scale products in bf16, fp32
+// accumulation, the prepared global scale applied before the bf16 round (the reference's
+// epilogue, sys/native/marlin/vendor/dense_template.h:1655-1658).
+//
+// The op streams N*K/2 + N*K/16 bytes once and is bound by HBM. One packed u32 is already
+// one thread's A fragment of mma.sync.m16n8k16 for a 16-row x 16-column weight block, so a
+// lane's 16-byte load covers four such blocks (64 output rows) of one 16-wide K tile, and its
+// eight scale bytes are 8 adjacent bytes. A CTA owns one 64-row tile of N and a K slice; its
+// eight warps take the slice's K tiles round-robin with all loads of a warp's share in flight
+// together, then add their accumulators through shared memory. K slices of one N tile meet in
+// the caller's `temporary` buffer; the slice that arrives last (a counter in the caller's
+// `locks`, which stay zero between launches) adds them in a fixed order. Nothing spins.
+#include <cuda_bf16.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+#include "fp4_codec.cuh"
+
+namespace mircuda_b200 {
+namespace marlin_dense {
+
+constexpr int kThreads = 256;
+constexpr int kWarps = 8;
+constexpr int kTileN = 64;
+constexpr int kTileK = 16;
+constexpr int kMaxTokens = 16;
+constexpr int kMaxTilesPerWarp = 8;        // K tiles whose loads one warp keeps in flight
+
+__device__ __forceinline__ void place_e2m1x8(uint32_t q, uint32_t (&out)[4]) {
+  out[3] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  out[2] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  out[1] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+  q <<= 4;
+  out[0] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+}
+
+__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                 uint32_t a2, uint32_t a3, uint32_t b0,
+                                                 uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// Prepared scale byte c = upper 8 bits (without sign) of the f16 v = s * factor * 128, or 0.
+// Returns v * 2^110 as a bf16 in both halves: exponent field (c >> 3) - 15 + 127 + 110, top
+// three mantissa bits c & 7, i.e. (c + 1776) << 4.
+__device__ __forceinline__ uint32_t scale_multiplier(uint32_t code) {
+  const uint32_t bits = code == 0u ? 0u : (code + 1776u) << 4;
+  return bits | (bits << 16);
+}
+
+template <int ROW_GROUPS>   // 1: tokens <= 8, 2: tokens <= 16
+__global__ void __launch_bounds__(kThreads)
+marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
+                          const uint4* __restrict__ weight, const uint8_t* __restrict__ scales,
+                          const float* __restrict__ global_scale,
+                          __nv_bfloat16* __restrict__ output, float* __restrict__ temporary,
+                          int* __restrict__ locks, int tokens, int n, int k, int slices,
+                          int tiles_per_slice) {
+  extern __shared__ __align__(16) uint8_t shared_raw[];
+  constexpr int kRows = ROW_GROUPS * 8;
+  // Activations of the K slice: [kRows][slice_k + 8] bf16 (padded against bank conflicts).
+  __nv_bfloat16* shared_x = reinterpret_cast<__nv_bfloat16*>(shared_raw);
+  const int x_stride = kWarps * kMaxTilesPerWarp * kTileK + 8;   // one round of K-elements
+  float* shared_sums = reinterpret_cast<float*>(shared_raw);   // reused after the main loop
+  __shared__ bool last_arrival;
+
+  const int tile_n = blockIdx.x;
+  const int slice = blockIdx.y;
+  const int tiles_n = n / kTileN;
+  const int first_tile_k = slice * tiles_per_slice;
+  const int tiles_k_total = k / kTileK;
+  const int tiles_here = min(tiles_per_slice, tiles_k_total - first_tile_k);
+  const int lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5;
+  const int group = lane >> 2;
+  const int quad = lane & 3;
+
+  float accumulator[4][ROW_GROUPS][4];
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+#pragma unroll
+      for (int item = 0; item < 4; ++item) accumulator[quarter][rows][item] = 0.0f;
+    }
+  }
+
+  // The slice is walked in rounds of up to 64 K tiles (8 per warp, 1024 K-elements).
+  constexpr int kRoundTiles = kWarps * kMaxTilesPerWarp;
+  for (int round_tile = 0; round_tile < tiles_here; round_tile += kRoundTiles) {
+    const int round_tiles = min(kRoundTiles, tiles_here - round_tile);
+    // This warp's K tiles of the round: warp, warp + 8, ... All their loads go out first.
+    uint4 words[kMaxTilesPerWarp];
+    uint2 scale_bytes[kMaxTilesPerWarp];
+#pragma unroll
+    for (int item = 0; item < kMaxTilesPerWarp; ++item) {
+      const int local_tile = warp + item * kWarps;
+      words[item] = make_uint4(0u, 0u, 0u, 0u);
+      scale_bytes[item] = make_uint2(0u, 0u);
+      if (local_tile < round_tiles) {
+        const int tile_k = first_tile_k + round_tile + local_tile;
+        words[item] = load_streaming_16(weight + (static_cast<size_t>(tile_k) * tiles_n + tile_n) * 32 + lane);
+        scale_bytes[item] = __ldg(reinterpret_cast<const uint2*>(
+            scales + (static_cast<size_t>(tile_k) * n + tile_n * kTileN) + group * 8));
+      }
+    }
+
+    __syncthreads();   // the previous round's activations are no longer needed
+    const int round_k = round_tiles * kTileK;
+    for (int index = threadIdx.x; index < kRows * round_k; index += kThreads) {
+      const int row = index / round_k;
+      const int column = index % round_k;
+      const int source = (first_tile_k + round_tile) * kTileK + column;
+      __nv_bfloat16 value = __float2bfloat16_rn(0.0f);
+      if (row < tokens) value = input[static_cast<size_t>(row) * k + source];
+      shared_x[row * x_stride + column] = value;
+    }
+    __syncthreads();
+
+#pragma unroll
+    for (int item = 0; item < kMaxTilesPerWarp; ++item) {
+      const int local_tile = warp + item * kWarps;
+      if (local_tile < round_tiles) {
+        // B fragments: activations of this K tile, token `group` of each row group.
+        uint32_t b[ROW_GROUPS][2];
+#pragma unroll
+        for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+          const __nv_bfloat16* x =
+              shared_x + (rows * 8 + group) * x_stride + local_tile * kTileK + quad * 2;
+          b[rows][0] = *reinterpret_cast<const uint32_t*>(x);
+          b[rows][1] = *reinterpret_cast<const uint32_t*>(x + 8);
+        }
+        const uint32_t quarter_words[4] = {words[item].x, words[item].y, words[item].z, words[item].w};
+        // Scale bytes of rows (g, g+8) for quarters 0..3 sit at byte offsets 0,2 | 1,3 | 4,6 | 5,7.
+        const uint32_t low = scale_bytes[item].x;
+        const uint32_t high = scale_bytes[item].y;
+        const uint32_t code[4][2] = {{low & 0xffu, (low >> 16) & 0xffu},
+                                     {(low >> 8) & 0xffu, low >> 24},
+                                     {high & 0xffu, (high >> 16) & 0xffu},
+                                     {(high >> 8) & 0xffu, high >> 24}};
+#pragma unroll
+        for (int quarter = 0; quarter < 4; ++quarter) {
+          uint32_t a[4];
+          place_e2m1x8(quarter_words[quarter], a);   // (a0,a1) (a4,a5) (a2,a3) (a6,a7)
+          const uint32_t upper = scale_multiplier(code[quarter][0]);   // row g
+          const uint32_t lower = scale_multiplier(code[quarter][1]);   // row g + 8
+          const uint32_t a0 = mul_bf16x2(a[0], upper);
+          const uint32_t a1 = mul_bf16x2(a[2], lower);
+          const uint32_t a2 = mul_bf16x2(a[1], upper);
+          const uint32_t a3 = mul_bf16x2(a[3], lower);
+#pragma unroll
+          for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+            mma_bf16_16x8x16(accumulator[quarter][rows], a0, a1, a2, a3, b[rows][0], b[rows][1]);
+          }
+        }
+      }
+    }
+  }
+  __syncthreads();   // everyone is done with shared_x; reuse the space for the warp sums
+
+  // shared_sums[warp][n_local 0..63][row 0..kRows-1]
+#pragma unroll
+  for (int quarter = 0; quarter < 4; ++quarter) {
+#pragma unroll
+    for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+      const int n_local = quarter * 16 + group;
+      const int row = rows * 8 + quad * 2;
+      float* base = shared_sums + (warp * kTileN + n_local) * kRows + row;
+      base[0] = accumulator[quarter][rows][0];
+      base[1] = accumulator[quarter][rows][1];
+      base[8 * kRows] = accumulator[quarter][rows][2];
+      base[8 * kRows + 1] = accumulator[quarter][rows][3];
+    }
+  }
+  __syncthreads();
+
+  // finish = prepared_global * 2^-110 undoes the 2^110 of the multiplier and the 2^-126 of
+  // the bit placement (2^-16 in total) together with the 2^119 / factor folded into the global.
+  const float finish = *global_scale * 7.70371977754894341e-34f;   // 2^-110
+  for (int index = threadIdx.x; index < kTileN * kRows; index += kThreads) {
+    const int n_local = index / kRows;
+    const int row = index % kRows;
+    float sum = 0.0f;
+#pragma unroll
+    for (int part = 0; part < kWarps; ++part) sum += shared_sums[(part * kTileN + n_local) * kRows + row];
+    const int column = tile_n * kTileN + n_local;
+    if (slices == 1) {
+      if (row < tokens) output[static_cast<size_t>(row) * n + column] = __float2bfloat16_rn(sum * finish);
+    } else {
+      temporary[(static_cast<size_t>(slice) * n + column) * kMaxTokens + row] = sum;
+    }
+  }
+  if (slices == 1) return;
+
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int arrived = atomicAdd(&locks[tile_n], 1);
+    last_arrival = arrived == slices - 1;
+    if (last_arrival) locks[tile_n] = 0;
+  }
+  __syncthreads();
+  if (!last_arrival) return;
+  __threadfence();
+  for (int index = threadIdx.x; index < kTileN * kRows; index += kThreads) {
+    const int n_local = index / kRows;
+    const int row = index % kRows;
+    const int column = tile_n * kTileN + n_local;
+    float total = 0.0f;
+    for (int part = 0; part < slices; ++part) {
+      total += __ldcg(temporary + (static_cast<size_t>(part) * n + column) * kMaxTokens + row);
+    }
+    if (row < tokens) output[static_cast<size_t>(row) * n + column] = __float2bfloat16_rn(total * finish);
+  }
+}
+
+}  // namespace marlin_dense
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* input,
+                                                  const void* weight, void* output,
+                                                  void* temporary, const void* scales,
+                                                  const float* global_scale, int tokens,
+                                                  int output_features, int input_features,
+                                                  int thread_config, void* locks,
+                                                  bool atomic_reduce) {
+  using namespace mircuda_b200::marlin_dense;
+  (void)thread_config;   // the tile geometry of this kernel is fixed
+  (void)atomic_reduce;   // the cross-slice reduction is always the ordered one
+  if (stream == nullptr || input == nullptr || weight == nullptr || output == nullptr ||
+      temporary == nullptr || scales == nullptr || global_scale == nullptr || locks == nullptr ||
+      tokens <= 0 || tokens > kMaxTokens || output_features <= 0 || input_features <= 0 ||
+      output_features % kTileN != 0 || input_features % kTileK != 0) {
+    return -1;
+  }
+  int device = 0, sm_count = 0;
+  int status = static_cast<int>(cudaGetDevice(&device));
+  if (status == 0) {
+    status = static_cast<int>(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
+  }
+  if (status != 0) return status;
+  const int tiles_n = output_features / kTileN;
+  const int tiles_k = input_features / kTileK;
+  // K slices: enough CTAs to fill the machine twice over, each with at least 8 K tiles.
+  // Slices need one lock per N tile (the caller provides one per SM) and
+  // slices * N * 16 floats of `temporary` (the caller provides 4096 per SM); a shape that
+  // does not fit runs unsliced.
+  int slices = (2 * sm_count + tiles_n - 1) / tiles_n;
+  if (slices > tiles_k / kWarps) slices = tiles_k / kWarps > 0 ? tiles_k / kWarps : 1;
+  const long long capacity = static_cast<long long>(sm_count) * 4096;
+  if (tiles_n > sm_count) slices = 1;
+  while (slices > 1 && static_cast<long long>(slices) * output_features * kMaxTokens > capacity) {
+    --slices;
+  }
+  int tiles_per_slice = (tiles_k + slices - 1) / slices;
+  slices = (tiles_k + tiles_per_slice - 1) / tiles_per_slice;
+  const dim3 grid(tiles_n, slices);
+  const int rows = tokens <= 8 ? 8 : 16;
+  const size_t x_bytes = static_cast<size_t>(rows) * (kWarps * kMaxTilesPerWarp * kTileK + 8) * 2;
+  const size_t sum_bytes = static_cast<size_t>(kWarps) * kTileN * rows * sizeof(float);
+  const size_t shared_bytes = x_bytes > sum_bytes ? x_bytes : sum_bytes;
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  if (tokens <= 8) {
+    marlin_nvfp4_dense_kernel<1><<<grid, kThreads, shared_bytes, cuda_stream>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<const uint4*>(weight),
+        static_cast<const uint8_t*>(scales), global_scale, static_cast<__nv_bfloat16*>(output),
+        static_cast<float*>(temporary), static_cast<int*>(locks), tokens, output_features,
+        input_features, slices, tiles_per_slice);
+  } else {
+    marlin_nvfp4_dense_kernel<2><<<grid, kThreads, shared_bytes, cuda_stream>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<const uint4*>(weight),
+        static_cast<const uint8_t*>(scales), global_scale, static_cast<__nv_bfloat16*>(output),
+        static_cast<float*>(temporary), static_cast<int*>(locks), tokens, output_features,
+        input_features, slices, tiles_per_slice);
+  }
+  return static_cast<int>(cudaPeekAtLastError());
+}
