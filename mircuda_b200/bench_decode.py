@@ -42,7 +42,16 @@ def _time(stream, launch, banks: int, cycles: int, repeats: int) -> float:
     with torch.cuda.graph(graph, stream=stream):
         for cycle in range(cycles):
             launch(cycle % banks)
-    graph.replay()
+    # Keep the GPU busy for a while first: these kernels are so short that a cold start would
+    # be timed at idle clocks.
+    warm = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    warm[0].record()
+    for _ in range(2000):
+        graph.replay()
+        warm[1].record()
+        warm[1].synchronize()
+        if warm[0].elapsed_time(warm[1]) > 150.0:
+            break
     torch.cuda.synchronize()
     samples = []
     for _ in range(repeats):
@@ -130,13 +139,17 @@ def bench_marlin(stream, n, k, m, cycles, repeats):
     return seconds, n * k * 0.5625 + m * k * 2 + m * n * 2, banks
 
 
-def run(ops, cycles: int, repeats: int, peak_gbs: float) -> dict:
+def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None) -> dict:
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
     results = []
     for op in ops:
         for name, n, k in SHAPES:
+            if shapes and name not in shapes:
+                continue
             for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1]):
+                if tokens and m not in tokens:
+                    continue
                 with torch.cuda.stream(stream):
                     if op == "nvfp4":
                         seconds, byte_count, banks = bench_nvfp4(stream, n, k, m, cycles, repeats)
@@ -161,8 +174,12 @@ def main() -> None:
     parser.add_argument("--repeats", type=int, default=5)
     parser.add_argument("--ops", default="nvfp4,fp4,dense,marlin")
     parser.add_argument("--peak-gbs", type=float, default=6551.4)
+    parser.add_argument("--shapes", default="", help="subset of qkv,o,gate_up,down (profiling runs)")
+    parser.add_argument("--tokens", default="", help="subset of 1,4,8 (profiling runs)")
     args = parser.parse_args()
-    summary = run(args.ops.split(","), args.cycles, args.repeats, args.peak_gbs)
+    summary = run(args.ops.split(","), args.cycles, args.repeats, args.peak_gbs,
+                  set(filter(None, args.shapes.split(","))),
+                  {int(t) for t in args.tokens.split(",") if t})
     by_op = {}
     for record in summary["results"]:
         by_op.setdefault(record["op"], []).append(record["frac_of_measured_hbm"])

@@ -6,18 +6,25 @@
 // (exact weight * scale products, fp32 accumulation, global scale before the bf16 round)
 // it follows.
 //
-// The op streams 0.5625*N*K bytes once and is bound by HBM, for every M up to 8: weights are
-// the 16-row operand of mma.sync.m16n8k16 (bf16 in, fp32 out) and the tokens ride its
-// 8-wide dimension, so decoding cost does not grow with M. A CTA owns 128 rows (one scale
-// row tile) x 512 K-elements; warp w owns K sub-range (w % 4) * 128 for rows (w / 4) * 64 and
-// keeps the activations of that sub-range in registers as ready-made B fragments. E2M1
-// codes become bf16 by bit placement (value * 2^-126, the zero-exponent codes as bf16
-// subnormals) and are multiplied by ue4m3(s) * 2^118 with one packed bf16 multiply, which
-// is exact; the epilogue undoes the 2^-8. Because a dot product does not care about the
-// order of its terms, the K order inside a 32-element chunk is whatever makes the bit
-// placement cheapest, and the activations are staged in shared memory in that same order.
-// K-slices meet through per-slice partial sums; the last slice to arrive for a row tile
-// (a counter, no spinning) adds them in a fixed order and writes bf16.
+// The op streams 0.5625*N*K bytes once and is bound by HBM, so the kernel is built around
+// keeping bytes in flight rather than around arithmetic:
+//  * a CTA owns one 128-row scale tile and a contiguous part of K; a producer warp streams
+//    that part in stages of 512 K-elements (a [128 x 256 B] weight box by TMA plus the eight
+//    512-byte scale atoms by one bulk copy) through a two-stage shared-memory ring, and two
+//    CTAs fit on an SM (four stages, 144 KB, in flight per SM; 256-element stages in a
+//    four-deep ring measured 20 % slower);
+//  * eight consumer warps turn E2M1 codes into f16x2 with the hardware conversion (one
+//    instruction per two weights; an earlier bit-placement version spent four instructions
+//    per weight and was bound by the integer pipe), multiply by the block scale with one
+//    exact packed f16 multiply and feed mma.sync.m16n8k16 with the weights on the 16-row side
+//    and the tokens on the 8-wide side, so the cost does not grow with M; activations are
+//    tiny, come straight from L2 into registers and are converted bf16 -> f16 there (exact
+//    for magnitudes in [2^-14, 65504], saturating above);
+//  * when N alone does not give enough CTAs, K is cut into 2, 4 or 8 parts that form a
+//    thread-block cluster; the parts' partial sums meet in the first CTA's shared memory
+//    (distributed shared memory, one cluster barrier) instead of in global memory.
+// Every mbarrier wait is bounded; the cluster barrier is reached on every path.
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_runtime_api.h>
 
@@ -25,239 +32,316 @@
 #include <new>
 
 #include "fp4_codec.cuh"
-#include "layout.cuh"
+#include "ptx.cuh"
+#include "ptx_pair.cuh"
+#include "tensor_map.hpp"
 
 namespace mircuda_b200 {
 namespace nvfp4_vector {
 
-constexpr int kThreads = 256;
+constexpr int kConsumerWarps = 8;
+constexpr int kThreads = (kConsumerWarps + 1) * 32;   // + one producer warp
 constexpr int kTileRows = 128;
-constexpr int kTileK = 512;
-constexpr int kAtomsPerTile = kTileK / 64;
-constexpr int kAtomStride = 512 + 8;
+constexpr int kStageK = 512;                          // K-elements per stage
+constexpr int kStageWeightBytes = kTileRows * kStageK / 2;   // 32 KB
+constexpr int kStageScaleBytes = (kStageK / 64) * 512;       // 8 atoms = 4 KB
+constexpr int kStages = 2;
+constexpr int kWarpsK = kStageK / 128;                // consumer warps side by side along K
+constexpr int kRowGroups = kConsumerWarps / kWarpsK;  // ... and along the rows
+constexpr int kRowsPerWarp = kTileRows / kRowGroups;
+constexpr int kSteps = kRowsPerWarp / 16;             // 16-row MMA steps per warp and stage
 constexpr int kMaxTokens = 8;
-constexpr int kChunks = kTileK / 32;                 // 32-element chunks per K-slice
-constexpr int kTokenStride = kTileK + 8;             // bf16 elements, padded
+constexpr int kMaxParts = 8;
 
 struct Plan {
-  int m;
-  int n;
-  int k;
-  int slices;
+  int m, n, k;
+  int parts;                 // K parts = cluster size along y
+  int device;
   cudaStream_t stream;
-  float* partials;          // [slices][row_tiles * 128][8]
-  unsigned int* counters;   // [row_tiles]
+  uint32_t* status;          // pinned; set when a bounded wait ran out
+  const void* cached_weight;
+  CUtensorMap weight_map;    // [N, K/2] bytes, box 256 B x 128 rows, no swizzle
 };
 
-// Position of element j (0..31) of a chunk in the staged order: word w = j / 8 holds nibbles
-// n0..n7; the decoder emits pairs (n0,n4) (n1,n5) (n2,n6) (n3,n7).
-__device__ __forceinline__ int staged_position(int j) {
-  const int word = j >> 3;
-  const int nibble = j & 7;
-  return word * 8 + (nibble & 3) * 2 + (nibble >> 2);
+struct SharedLayout {
+  static constexpr int kWeights = 0;
+  static constexpr int kSums = 0;      // [kWarpsK][128][8] f32, reuses the ring after the main loop
+  static constexpr int kScales = kStages * kStageWeightBytes;
+  static constexpr int kParts = kScales + kStages * kStageScaleBytes;            // [8][128][8] f32
+  static constexpr int kBarriers = kParts + kMaxParts * kTileRows * kMaxTokens * 4;
+  static constexpr int kBytes = kBarriers + 2 * kStages * 8 + 16 + 1024;         // + alignment slack
+  static_assert(kWarpsK * kTileRows * kMaxTokens * 4 <= kStages * kStageWeightBytes, "sums fit the ring");
+  static_assert(2 * kBytes <= 232448, "two CTAs per SM");
+};
+
+// Eight E2M1 codes (one u32, even k in the low nibble of each byte) -> four f16x2 in K order,
+// with the sm_100a conversion instruction: one instruction per two weights.
+__device__ __forceinline__ void decode_e2m1x8_bits(uint32_t codes, uint32_t (&out)[4]) {
+  asm("{\n\t"
+      ".reg .b8 b0, b1, b2, b3;\n\t"
+      "mov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %3, b3;\n\t"
+      "}\n"
+      : "=r"(out[0]), "=r"(out[1]), "=r"(out[2]), "=r"(out[3])
+      : "r"(codes));
 }
 
-// Eight E2M1 codes -> four bf16x2 holding value * 2^-126: sign to bit 15, the three
-// exponent/mantissa bits to bf16 bits 8..6. out[p] = (nibble p, nibble p + 4).
-__device__ __forceinline__ void place_e2m1x8(uint32_t q, uint32_t (&out)[4]) {
-  out[3] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  out[2] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  out[1] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
-  q <<= 4;
-  out[0] = (q & 0x80008000u) | ((q & 0x70007000u) >> 6);
+// Two E4M3 codes (low 16 bits) -> f16x2, exact.
+__device__ __forceinline__ uint32_t decode_e4m3x2(uint32_t two_codes) {
+  uint32_t pair;
+  asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(pair) : "h"(static_cast<uint16_t>(two_codes)));
+  return pair;
 }
 
-__device__ __forceinline__ uint32_t mul_bf16x2(uint32_t a, uint32_t b) {
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
   uint32_t d;
-  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
   return d;
 }
 
-__device__ __forceinline__ void mma_bf16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1,
-                                                 uint32_t a2, uint32_t a3, uint32_t b0,
-                                                 uint32_t b1) {
+// Two bf16 -> two f16 (round to nearest, saturating at +-65504). Exact for every value whose
+// magnitude lies in [2^-14, 65504]; smaller ones keep an absolute error below 2^-25.
+__device__ __forceinline__ uint32_t bf16x2_to_f16x2(uint32_t pair) {
+  uint32_t d;
+  const float low = __uint_as_float(pair << 16);
+  const float high = __uint_as_float(pair & 0xffff0000u);
+  asm("cvt.rn.satfinite.f16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(high), "f"(low));
+  return d;
+}
+
+__device__ __forceinline__ void mma_f16_16x8x16(float (&d)[4], uint32_t a0, uint32_t a1,
+                                                uint32_t a2, uint32_t a3, uint32_t b0,
+                                                uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 "
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 "
       "{%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// ue4m3(code) * 2^118 as a bf16 replicated in both halves (exact: 4 significant bits).
-__device__ __forceinline__ uint32_t scale_multiplier(uint8_t code) {
-  const float scaled = decode_ue4m3(code) * 3.32306998946228968e35f;  // 2^118
-  const uint32_t high = __float_as_uint(scaled) >> 16;
-  return high | (high << 16);
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+  return d;
 }
 
 __global__ void __launch_bounds__(kThreads)
-nvfp4_vector_kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __restrict__ weight,
-       const uint8_t* __restrict__ weight_scales, __nv_bfloat16* __restrict__ output,
-       float* __restrict__ partials, unsigned int* __restrict__ counters, int m, int n, int k,
-       int slices, float global_scale) {
-  __shared__ __align__(16) uint8_t shared_scales[kAtomsPerTile * kAtomStride];
-  __shared__ __align__(16) __nv_bfloat16 shared_x[kMaxTokens * kTokenStride];
-  __shared__ __align__(16) float shared_sums[4][kTileRows][kMaxTokens];
-  __shared__ bool last_arrival;
+nvfp4_vector_kernel(const __grid_constant__ CUtensorMap weight_map,
+                    const __nv_bfloat16* __restrict__ input,
+                    const uint8_t* __restrict__ weight_scales,
+                    __nv_bfloat16* __restrict__ output, int m, int n, int k, int parts,
+                    float global_scale, uint32_t* __restrict__ status) {
+  extern __shared__ uint8_t dynamic_shared[];
+  const uint32_t misalignment = ptx::smem_address(dynamic_shared) & 1023u;
+  uint8_t* shared = dynamic_shared + ((1024u - misalignment) & 1023u);
+  uint8_t* shared_weights = shared + SharedLayout::kWeights;
+  uint8_t* shared_scales = shared + SharedLayout::kScales;
+  float* shared_sums = reinterpret_cast<float*>(shared + SharedLayout::kSums);
+  float* shared_parts = reinterpret_cast<float*>(shared + SharedLayout::kParts);
+  uint64_t* full = reinterpret_cast<uint64_t*>(shared + SharedLayout::kBarriers);
+  uint64_t* empty = full + kStages;
+  volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(empty + kStages);
 
   const int row_tile = blockIdx.x;
-  const int slice = blockIdx.y;
-  const int k_begin = slice * kTileK;
+  const int part = blockIdx.y;                       // == rank inside the cluster
+  const int stages_total = (k + kStageK - 1) / kStageK;
+  const int stages_per_part = (stages_total + parts - 1) / parts;
+  const int first_stage = part * stages_per_part;
+  const int my_stages = max(0, min(stages_per_part, stages_total - first_stage));
   const int atoms_k = k / 64;
-  const int lane = threadIdx.x & 31;
   const int warp = threadIdx.x >> 5;
-  const int group = lane >> 2;                     // row inside a 16-row step / token index
-  const int quad = lane & 3;                       // 32-element chunk inside the warp's range
-  const int warp_k = warp & 3;
-  const int warp_rows = warp >> 2;
-  const int chunk = warp_k * 4 + quad;             // chunk of this thread inside the slice
-  const int element = k_begin + chunk * 32;
-  const bool active = element < k;
+  const int lane = threadIdx.x & 31;
 
-  // All weight loads of this thread first: 4 row steps x 2 rows x 16 bytes.
-  uint4 packed[4][2];
-#pragma unroll
-  for (int step = 0; step < 4; ++step) {
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int row = row_tile * kTileRows + warp_rows * 64 + step * 16 + half * 8 + group;
-      packed[step][half] = make_uint4(0u, 0u, 0u, 0u);
-      if (active && row < n) {
-        packed[step][half] =
-            load_streaming_16(weight + (static_cast<size_t>(row) * k + element) / 2);
-      }
-    }
-  }
-
-  // Scale atoms of the tile (whole, coalesced) and the activation slice in staged order.
-  {
-    const int atom = threadIdx.x >> 5;
-    const int offset = (threadIdx.x & 31) * 16;
-    const int atom_column = k_begin / 64 + atom;
-    uint4 value = make_uint4(0u, 0u, 0u, 0u);
-    if (atom_column < atoms_k) {
-      value = __ldg(reinterpret_cast<const uint4*>(
-          weight_scales + (static_cast<size_t>(row_tile) * atoms_k + atom_column) * 512 + offset));
-    }
-    *reinterpret_cast<uint2*>(shared_scales + atom * kAtomStride + offset) =
-        make_uint2(value.x, value.y);
-    *reinterpret_cast<uint2*>(shared_scales + atom * kAtomStride + offset + 8) =
-        make_uint2(value.z, value.w);
-  }
-  for (int index = threadIdx.x; index < kMaxTokens * kTileK; index += kThreads) {
-    const int token = index / kTileK;
-    const int offset = index % kTileK;
-    const int source = k_begin + offset;
-    __nv_bfloat16 value = __float2bfloat16_rn(0.0f);
-    if (token < m && source < k) value = input[static_cast<size_t>(token) * k + source];
-    shared_x[token * kTokenStride + (offset & ~31) + staged_position(offset & 31)] = value;
-  }
-  __syncthreads();
-
-  // B fragments of this thread: token `group`, chunk `chunk`, 32 staged elements = 16 words.
-  uint32_t b[16];
-  {
-    const uint4* source =
-        reinterpret_cast<const uint4*>(shared_x + group * kTokenStride + chunk * 32);
-#pragma unroll
-    for (int part = 0; part < 4; ++part) {
-      const uint4 value = source[part];
-      b[part * 4 + 0] = value.x;
-      b[part * 4 + 1] = value.y;
-      b[part * 4 + 2] = value.z;
-      b[part * 4 + 3] = value.w;
-    }
-  }
-
-  const int scale_atom = chunk >> 1;
-  const int scale_byte = (chunk & 1) * 2;
-#pragma unroll
-  for (int step = 0; step < 4; ++step) {
-    float accumulator[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    uint32_t multiplier[2][2];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int row_in_tile = warp_rows * 64 + step * 16 + half * 8 + group;
-      const uint16_t two = *reinterpret_cast<const uint16_t*>(
-          shared_scales + scale_atom * kAtomStride + (row_in_tile & 31) * 16 +
-          (row_in_tile >> 5) * 4 + scale_byte);
-      multiplier[half][0] = scale_multiplier(static_cast<uint8_t>(two & 0xffu));
-      multiplier[half][1] = scale_multiplier(static_cast<uint8_t>(two >> 8));
-    }
-    const uint32_t words[2][4] = {
-        {packed[step][0].x, packed[step][0].y, packed[step][0].z, packed[step][0].w},
-        {packed[step][1].x, packed[step][1].y, packed[step][1].z, packed[step][1].w}};
-#pragma unroll
-    for (int word = 0; word < 4; ++word) {
-      uint32_t low[4], high[4];
-      place_e2m1x8(words[0][word], low);    // row `group`
-      place_e2m1x8(words[1][word], high);   // row `group + 8`
-      const uint32_t scale_low = multiplier[0][word >> 1];
-      const uint32_t scale_high = multiplier[1][word >> 1];
-#pragma unroll
-      for (int pair = 0; pair < 2; ++pair) {
-        // One MMA: this thread's k-slots (2t, 2t+1) and (2t+8, 2t+9) are staged pairs
-        // 2*pair and 2*pair+1 of the word, for both rows.
-        mma_bf16_16x8x16(accumulator, mul_bf16x2(low[2 * pair], scale_low),
-                         mul_bf16x2(high[2 * pair], scale_high),
-                         mul_bf16x2(low[2 * pair + 1], scale_low),
-                         mul_bf16x2(high[2 * pair + 1], scale_high), b[word * 4 + 2 * pair],
-                         b[word * 4 + 2 * pair + 1]);
-      }
-    }
-    // accumulator: rows (group, group + 8) x tokens (2*quad, 2*quad + 1)
-    const int row_in_tile = warp_rows * 64 + step * 16 + group;
-    *reinterpret_cast<float2*>(&shared_sums[warp_k][row_in_tile][2 * quad]) =
-        make_float2(accumulator[0], accumulator[1]);
-    *reinterpret_cast<float2*>(&shared_sums[warp_k][row_in_tile + 8][2 * quad]) =
-        make_float2(accumulator[2], accumulator[3]);
-  }
-  __syncthreads();
-
-  // 128 rows x 8 tokens: four threads... one (row, token pair-of-four) per thread.
-  const float finish = global_scale * 256.0f;  // undo the 2^-8 left by the scale multiplier
-  for (int index = threadIdx.x; index < kTileRows * kMaxTokens; index += kThreads) {
-    const int row_in_tile = index / kMaxTokens;
-    const int token = index % kMaxTokens;
-    const float sum = (shared_sums[0][row_in_tile][token] + shared_sums[1][row_in_tile][token]) +
-                      (shared_sums[2][row_in_tile][token] + shared_sums[3][row_in_tile][token]);
-    const int row = row_tile * kTileRows + row_in_tile;
-    if (slices == 1) {
-      if (row < n && token < m) {
-        output[static_cast<size_t>(token) * n + row] = __float2bfloat16_rn(sum * finish);
-      }
-    } else {
-      partials[(static_cast<size_t>(slice) * gridDim.x * kTileRows + row) * kMaxTokens + token] =
-          sum;
-    }
-  }
-  if (slices == 1) return;
-
-  __threadfence();
-  __syncthreads();
   if (threadIdx.x == 0) {
-    const unsigned int arrived = atomicAdd(&counters[row_tile], 1u);
-    last_arrival = arrived == static_cast<unsigned int>(slices - 1);
-    if (last_arrival) counters[row_tile] = 0u;
+    for (int stage = 0; stage < kStages; ++stage) {
+      ptx::mbarrier_init(&full[stage], 1);
+      ptx::mbarrier_init(&empty[stage], kConsumerWarps);
+    }
+    *abort = 0u;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensor_map(&weight_map);
   }
   __syncthreads();
-  if (!last_arrival) return;
-  __threadfence();
-  for (int index = threadIdx.x; index < kTileRows * kMaxTokens; index += kThreads) {
-    const int row_in_tile = index / kMaxTokens;
-    const int token = index % kMaxTokens;
-    const int row = row_tile * kTileRows + row_in_tile;
-    float total = 0.0f;
-    for (int part = 0; part < slices; ++part) {
-      total += __ldcg(partials +
-                      (static_cast<size_t>(part) * gridDim.x * kTileRows + row) * kMaxTokens + token);
+
+  if (warp == kConsumerWarps) {
+    // --------------------------------------------------------------------- producer
+    if (ptx::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      for (int index = 0; index < my_stages; ++index) {
+        if (!ptx::mbarrier_wait(&empty[stage], phase ^ 1u, abort)) break;
+        const int global_stage = first_stage + index;
+        const int atoms_here = min(kStageK / 64, atoms_k - global_stage * (kStageK / 64));
+        ptx::mbarrier_arrive_expect_tx(&full[stage], kStageWeightBytes + atoms_here * 512);
+        ptx::tma_load_2d(shared_weights + stage * kStageWeightBytes, &weight_map, &full[stage],
+                         global_stage * (kStageK / 2), row_tile * kTileRows);
+        ptx::bulk_load(shared_scales + stage * kStageScaleBytes,
+                       weight_scales + (static_cast<size_t>(row_tile) * atoms_k +
+                                        static_cast<size_t>(global_stage) * (kStageK / 64)) * 512,
+                       atoms_here * 512, &full[stage]);
+        if (++stage == kStages) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      if (*abort != 0u) {
+        for (int spin = 0; spin < 256; ++spin) __nanosleep(1000);
+      }
     }
-    if (row < n && token < m) {
-      output[static_cast<size_t>(token) * n + row] = __float2bfloat16_rn(total * finish);
+  } else {
+    // -------------------------------------------------------------------- consumers
+    const int group = lane >> 2;                     // weight row inside a 16-row step / token
+    const int quad = lane & 3;
+    const int warp_k = warp % kWarpsK;               // 128-element K sub-range of the stage
+    const int warp_rows = warp / kWarpsK;            // kRowsPerWarp rows of the tile
+    const int chunk = warp_k * 4 + quad;             // this thread's 32-element chunk
+    float accumulator[kSteps][4];
+#pragma unroll
+    for (int step = 0; step < kSteps; ++step) {
+#pragma unroll
+      for (int item = 0; item < 4; ++item) accumulator[step][item] = 0.0f;
+    }
+    uint32_t stage = 0, phase = 0;
+    for (int index = 0; index < my_stages; ++index) {
+      const int element = (first_stage + index) * kStageK + chunk * 32;
+      // B fragments first (from L2; independent of the stage's arrival): token `group`,
+      // 32 consecutive activations as f16x2 pairs in K order.
+      uint32_t b[16];
+      if (group < m && element < k) {
+        const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(group) * k + element);
+#pragma unroll
+        for (int word = 0; word < 4; ++word) {
+          const uint4 v = __ldg(source + word);       // x0..x7 as (x0,x1) (x2,x3) (x4,x5) (x6,x7)
+          b[word * 4 + 0] = bf16x2_to_f16x2(v.x);
+          b[word * 4 + 1] = bf16x2_to_f16x2(v.y);
+          b[word * 4 + 2] = bf16x2_to_f16x2(v.z);
+          b[word * 4 + 3] = bf16x2_to_f16x2(v.w);
+        }
+      } else {
+#pragma unroll
+        for (int item = 0; item < 16; ++item) b[item] = 0u;
+      }
+      if (!ptx::mbarrier_wait(&full[stage], phase, abort)) break;
+      const uint8_t* weights = shared_weights + stage * kStageWeightBytes;
+      const uint8_t* scales = shared_scales + stage * kStageScaleBytes;
+      const bool active = element < k;
+#pragma unroll
+      for (int step = 0; step < kSteps; ++step) {
+        const int row_low = warp_rows * kRowsPerWarp + step * 16 + group;
+        const int row_high = row_low + 8;
+        const uint4 packed_low = *reinterpret_cast<const uint4*>(weights + row_low * (kStageK / 2) + chunk * 16);
+        const uint4 packed_high = *reinterpret_cast<const uint4*>(weights + row_high * (kStageK / 2) + chunk * 16);
+        const uint32_t two_low = *reinterpret_cast<const uint16_t*>(
+            scales + (chunk >> 1) * 512 + (row_low & 31) * 16 + (row_low >> 5) * 4 + (chunk & 1) * 2);
+        const uint32_t two_high = *reinterpret_cast<const uint16_t*>(
+            scales + (chunk >> 1) * 512 + (row_high & 31) * 16 + (row_high >> 5) * 4 + (chunk & 1) * 2);
+        // Both block scales of the chunk in one conversion (UE4M3 is exact in f16), then each
+        // broadcast to both halves of a register.
+        // A chunk past the end of K holds zero codes (TMA fill) but stale scale bytes: force
+        // those scales to zero too. The MMAs themselves run in every lane (mma.sync needs the
+        // whole warp converged).
+        const uint32_t scale_mask = active ? 0x7f7fu : 0u;
+        const uint32_t both_low = decode_e4m3x2(two_low & scale_mask);
+        const uint32_t both_high = decode_e4m3x2(two_high & scale_mask);
+        const uint32_t multiplier_low[2] = {prmt(both_low, both_low, 0x1010u), prmt(both_low, both_low, 0x3232u)};
+        const uint32_t multiplier_high[2] = {prmt(both_high, both_high, 0x1010u),
+                                             prmt(both_high, both_high, 0x3232u)};
+        const uint32_t words_low[4] = {packed_low.x, packed_low.y, packed_low.z, packed_low.w};
+        const uint32_t words_high[4] = {packed_high.x, packed_high.y, packed_high.z, packed_high.w};
+#pragma unroll
+        for (int word = 0; word < 4; ++word) {
+          // Eight codes -> (w0,w1) (w2,w3) (w4,w5) (w6,w7) as f16x2, exact; times the block
+          // scale, still exact in f16 (6 significant bits, magnitude within [2^-10, 2688]).
+          uint32_t low[4], high[4];
+          decode_e2m1x8_bits(words_low[word], low);
+          decode_e2m1x8_bits(words_high[word], high);
+          const uint32_t scale_low = multiplier_low[word >> 1];
+          const uint32_t scale_high = multiplier_high[word >> 1];
+#pragma unroll
+          for (int pair = 0; pair < 2; ++pair) {
+            mma_f16_16x8x16(accumulator[step], mul_f16x2(low[2 * pair], scale_low),
+                            mul_f16x2(high[2 * pair], scale_high),
+                            mul_f16x2(low[2 * pair + 1], scale_low),
+                            mul_f16x2(high[2 * pair + 1], scale_high), b[word * 4 + 2 * pair],
+                            b[word * 4 + 2 * pair + 1]);
+          }
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::mbarrier_arrive(&empty[stage]);
+      if (++stage == kStages) {
+        stage = 0;
+        phase ^= 1u;
+      }
+    }
+    // All consumer warps are done with the ring before the sums overwrite it.
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
+    // accumulator[step]: rows (group, group + 8) of the step x tokens (2*quad, 2*quad + 1)
+#pragma unroll
+    for (int step = 0; step < kSteps; ++step) {
+      const int row = warp_rows * kRowsPerWarp + step * 16 + group;
+      float* base = shared_sums + (warp_k * kTileRows + row) * kMaxTokens + 2 * quad;
+      *reinterpret_cast<float2*>(base) = make_float2(accumulator[step][0], accumulator[step][1]);
+      *reinterpret_cast<float2*>(base + 8 * kMaxTokens) =
+          make_float2(accumulator[step][2], accumulator[step][3]);
     }
   }
+  __syncthreads();
+
+  // CTA partial [128 rows][8 tokens] = sum over the K sub-ranges; it goes to slot `part`
+  // of the first CTA's `shared_parts` (its own shared memory when there is one part).
+  const uint32_t slot_base = ptx::smem_address(shared_parts + part * kTileRows * kMaxTokens);
+  const uint32_t remote_base = parts > 1 ? ptx::map_to_cta(slot_base, 0u) : slot_base;
+  for (int index = threadIdx.x; index < kTileRows * kMaxTokens; index += kThreads) {
+    float sum = shared_sums[index];
+#pragma unroll
+    for (int sub = 1; sub < kWarpsK; ++sub) sum += shared_sums[sub * kTileRows * kMaxTokens + index];
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote_base + index * 4), "f"(sum) : "memory");
+  }
+  if (parts > 1) {
+    ptx::cluster_arrive();
+    ptx::cluster_wait();
+  } else {
+    __syncthreads();
+  }
+  if (part == 0) {
+    const float finish = global_scale;
+    for (int index = threadIdx.x; index < kTileRows * kMaxTokens; index += kThreads) {
+      const int row = row_tile * kTileRows + index / kMaxTokens;
+      const int token = index % kMaxTokens;
+      float total = 0.0f;
+      for (int slot = 0; slot < parts; ++slot) total += shared_parts[slot * kTileRows * kMaxTokens + index];
+      if (row < n && token < m) {
+        output[static_cast<size_t>(token) * n + row] = __float2bfloat16_rn(total * finish);
+      }
+    }
+  }
+  if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
+}
+
+// K parts (cluster size): the choice that leaves the fewest idle CTA slots. Two CTAs fit on
+// an SM; with `parts` parts there are row_tiles * parts CTAs of ceil(stages / parts) stages,
+// and the kernel lasts as long as the slot that gets the most of them.
+int parts_for(int n, int k, int sm_count) {
+  const int row_tiles = (n + kTileRows - 1) / kTileRows;
+  const int stages = (k + kStageK - 1) / kStageK;
+  const int slots = 2 * sm_count;
+  int best = 1;
+  long long best_length = 0;
+  for (int parts = 1; parts <= kMaxParts && parts <= stages; parts *= 2) {
+    const int per_cta = (stages + parts - 1) / parts;
+    const long long ctas = static_cast<long long>(row_tiles) * parts;
+    const long long rounds = (ctas + slots - 1) / slots;
+    const long long length = rounds * per_cta;
+    if (parts == 1 || length < best_length) {
+      best = parts;
+      best_length = length;
+    }
+  }
+  return best;
 }
 
 }  // namespace nvfp4_vector
@@ -275,30 +359,28 @@ extern "C" int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* strea
   plan->m = m;
   plan->n = n;
   plan->k = k;
-  plan->slices = (k + kTileK - 1) / kTileK;
   plan->stream = static_cast<cudaStream_t>(stream);
-  const size_t row_tiles = (static_cast<size_t>(n) + kTileRows - 1) / kTileRows;
-  int status = 0;
-  if (plan->slices > 1) {
-    status = static_cast<int>(cudaMallocAsync(
-        reinterpret_cast<void**>(&plan->partials),
-        static_cast<size_t>(plan->slices) * row_tiles * kTileRows * kMaxTokens * sizeof(float),
-        plan->stream));
-    if (status == 0) {
-      status = static_cast<int>(cudaMallocAsync(reinterpret_cast<void**>(&plan->counters),
-                                                row_tiles * sizeof(unsigned int), plan->stream));
-    }
-    if (status == 0) {
-      status = static_cast<int>(
-          cudaMemsetAsync(plan->counters, 0, row_tiles * sizeof(unsigned int), plan->stream));
-    }
+  int sm_count = 0;
+  int status = static_cast<int>(cudaGetDevice(&plan->device));
+  if (status == 0) {
+    status = static_cast<int>(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, plan->device));
+  }
+  if (status == 0) {
+    status = static_cast<int>(cudaHostAlloc(reinterpret_cast<void**>(&plan->status),
+                                            sizeof(uint32_t), cudaHostAllocMapped));
+  }
+  if (status == 0) {
+    status = static_cast<int>(cudaFuncSetAttribute(nvfp4_vector_kernel,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   SharedLayout::kBytes));
   }
   if (status != 0) {
-    if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
-    if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
+    if (plan->status != nullptr) cudaFreeHost(plan->status);
     delete plan;
     return status;
   }
+  *plan->status = 0u;
+  plan->parts = parts_for(n, k, sm_count);
   *output = plan;
   return 0;
 }
@@ -306,6 +388,7 @@ extern "C" int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* strea
 extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const void* input,
                                                  const void* weight, const void* weight_scales,
                                                  void* output, float global_scale) {
+  using namespace mircuda_b200;
   using namespace mircuda_b200::nvfp4_vector;
   if (raw == nullptr || stream == nullptr || input == nullptr || weight == nullptr ||
       weight_scales == nullptr || output == nullptr) {
@@ -314,22 +397,46 @@ extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const 
   auto* plan = static_cast<Plan*>(raw);
   auto cuda_stream = static_cast<cudaStream_t>(stream);
   if (cuda_stream != plan->stream) return -1;
-  if (((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(weight_scales)) & 15u) !=
-      0u) {
+  if (*static_cast<volatile uint32_t*>(plan->status) != 0u) return -3;
+  if (((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(weight_scales) |
+        reinterpret_cast<uintptr_t>(input)) & 15u) != 0u) {
     return -1;
   }
-  const dim3 grid((plan->n + kTileRows - 1) / kTileRows, plan->slices);
-  nvfp4_vector_kernel<<<grid, kThreads, 0, cuda_stream>>>(
-      static_cast<const __nv_bfloat16*>(input), static_cast<const uint8_t*>(weight),
-      static_cast<const uint8_t*>(weight_scales), static_cast<__nv_bfloat16*>(output),
-      plan->partials, plan->counters, plan->m, plan->n, plan->k, plan->slices, global_scale);
-  return static_cast<int>(cudaPeekAtLastError());
+  if (weight != plan->cached_weight) {
+    EncodeTiled encode = encode_tiled_entry();
+    if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
+    const cuuint64_t dimensions[2] = {static_cast<cuuint64_t>(plan->k / 2), static_cast<cuuint64_t>(plan->n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(plan->k / 2)};
+    const cuuint32_t box[2] = {kStageK / 2, kTileRows};
+    const cuuint32_t element_strides[2] = {1u, 1u};
+    const int status = static_cast<int>(encode(
+        &plan->weight_map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2u, const_cast<void*>(weight), dimensions,
+        strides, box, element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    if (status != 0) return status;
+    plan->cached_weight = weight;
+  }
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3((plan->n + kTileRows - 1) / kTileRows, plan->parts, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = SharedLayout::kBytes;
+  config.stream = cuda_stream;
+  cudaLaunchAttribute attribute = {};
+  attribute.id = cudaLaunchAttributeClusterDimension;
+  attribute.val.clusterDim.x = 1;
+  attribute.val.clusterDim.y = plan->parts;
+  attribute.val.clusterDim.z = 1;
+  config.attrs = &attribute;
+  config.numAttrs = 1;
+  return static_cast<int>(cudaLaunchKernelEx(
+      &config, nvfp4_vector_kernel, plan->weight_map, static_cast<const __nv_bfloat16*>(input),
+      static_cast<const uint8_t*>(weight_scales), static_cast<__nv_bfloat16*>(output), plan->m,
+      plan->n, plan->k, plan->parts, global_scale, plan->status));
 }
 
 extern "C" void mircuda_b200_nvfp4_vector_destroy(void* raw) {
   auto* plan = static_cast<mircuda_b200::nvfp4_vector::Plan*>(raw);
   if (plan == nullptr) return;
-  if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
-  if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
+  if (plan->status != nullptr) cudaFreeHost(plan->status);
   delete plan;
 }

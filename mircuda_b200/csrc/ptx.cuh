@@ -66,18 +66,30 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t* barrier, uint32_t pa
   return done != 0;
 }
 
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t now;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+  return now;
+}
+
 // Polls until the phase with the given parity completes, `abort` becomes non-zero, or the
-// poll budget runs out. Returns false in the last two cases (and raises `abort` itself when
+// time budget runs out. Returns false in the last two cases (and raises `abort` itself when
 // the budget ran out), so that every role of the CTA leaves its loop and the kernel can
-// finish cleanly. One try_wait already blocks for a hardware-defined time slice, so the
-// budget corresponds to far longer than any legitimate wait.
-constexpr uint32_t kWaitPolls = 1u << 20;
+// finish cleanly. The bound is wall time, not a poll count: one try_wait may itself block
+// for a hardware-defined slice that can be as long as a millisecond. Half a second is
+// orders of magnitude beyond any legitimate wait in these kernels.
+constexpr uint64_t kWaitBudgetNs = 500ull * 1000ull * 1000ull;
 
 __device__ __forceinline__ bool mbarrier_wait(uint64_t* barrier, uint32_t parity,
                                               volatile uint32_t* abort) {
-  for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
+  if (mbarrier_try_wait(barrier, parity)) return true;
+  const uint64_t start = global_timer_ns();
+  for (uint32_t poll = 1;; ++poll) {
     if (mbarrier_try_wait(barrier, parity)) return true;
-    if ((poll & 63u) == 63u && *abort != 0u) return false;
+    if ((poll & 15u) == 0u) {
+      if (*abort != 0u) return false;
+      if (global_timer_ns() - start > kWaitBudgetNs) break;
+    }
   }
   *abort = 1u;
   return false;

@@ -62,12 +62,7 @@ __device__ __forceinline__ bool mbarrier_try_wait_cluster(uint64_t* barrier, uin
 // Bounded wait on a barrier of this CTA whose arrivals may come from the peer CTA.
 __device__ __forceinline__ bool mbarrier_wait_cluster(uint64_t* barrier, uint32_t parity,
                                                       volatile uint32_t* abort) {
-  for (uint32_t poll = 0; poll < kWaitPolls; ++poll) {
-    if (mbarrier_try_wait_cluster(barrier, parity)) return true;
-    if ((poll & 63u) == 63u && *abort != 0u) return false;
-  }
-  *abort = 1u;
-  return false;
+  return mbarrier_wait(barrier, parity, abort);
 }
 
 // Tiled loads into this CTA's shared memory whose byte count is reported to an mbarrier
