@@ -58,6 +58,18 @@ int mircuda_mxfp8_tc_execute(void* plan, void* stream, const void* a, const void
                              const void* b, const void* b_scales, void* c);
 void mircuda_mxfp8_tc_destroy(void* plan);
 
+/* The same GEMM fused with the all-gather of a column-sharded linear. NEW (the reference is
+ * single-GPU). The plan's n is this GPU's shard width; instead of a local C the epilogue
+ * stores every tile into the full-width output [m, row_stride] of each of `output_count`
+ * GPUs (<= 8, the caller's own buffer among them) at column `column_offset`, through
+ * peer-mapped device pointers (CUDA IPC / symmetric memory), with plain stores over NVLink.
+ * The caller orders the peers' reads after this launch (a cross-GPU barrier on the stream).
+ * Needs m > 128 and n, row_stride, column_offset multiples of 8; -1 otherwise. */
+int mircuda_b200_mxfp8_tc_execute_gather(void* plan, void* stream, const void* a,
+                                         const void* a_scales, const void* b,
+                                         const void* b_scales, void* const* outputs,
+                                         int output_count, int row_stride, int column_offset);
+
 /* Weight-only MXFP8 (bf16 activations, row-major [n, k/32] E8M0 scales, weights as
  * little-endian u32 words), any token count. Replaces `mircuda_mxfp8_bf16` and
  * `mircuda_mxfp8_bf16_tiled` (kernels/mxfp8.cu:111-217) with their launches in

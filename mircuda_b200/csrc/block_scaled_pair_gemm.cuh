@@ -77,7 +77,9 @@ struct Layout {
   static constexpr uint32_t kBarrierOffset = kSfbOffset + STAGES * kSfbBytes;
   static constexpr uint32_t kBarriers = 2 * STAGES + 2 * ACC_STAGES;
   static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
-  static constexpr uint32_t kDynamicBytes = kMiscOffset + 16 + 1024;
+  // Epilogue transpose buffers: 32 rows x 128 bytes for each of the four epilogue warps.
+  static constexpr uint32_t kStagingOffset = (kMiscOffset + 16 + 127) / 128 * 128;
+  static constexpr uint32_t kDynamicBytes = kStagingOffset + 4 * 4096 + 1024;
   // Tensor memory: accumulators, then as many scale buffers as fit (at most one per stage).
   // With several buffers the copy of the next stage's scales never has to wait for the
   // MMAs that still read the previous stage's.
@@ -91,8 +93,20 @@ struct Layout {
   static_assert(kDynamicBytes <= 232448, "shared memory budget");
 };
 
+// Fused GEMM + all-gather for column-sharded linears: when `count` is non-zero the epilogue
+// does not write C[M, n] locally but stores every tile into the full-width output
+// [M, row_stride] of each of `count` GPUs (this GPU's own buffer among them) at column
+// `column_offset`, with ordinary stores through peer-mapped pointers. The transfer over
+// NVLink then overlaps the MMAs of the following tiles and no separate collective runs.
+struct Gather {
+  __nv_bfloat16* outputs[8];
+  uint32_t count;
+  uint32_t row_stride;
+  uint32_t column_offset;
+};
+
 struct Maps {
-  CUtensorMap a;      // [M, K bytes], box 128 rows x 128 bytes, 128-byte swizzle
+  CUtensorMap a;     // [M, K bytes], box 128 rows x 128 bytes, 128-byte swizzle
   CUtensorMap b;      // [N, K bytes], box BN/2 rows x 128 bytes
   CUtensorMap sfa;    // scales as u32 [row tiles][K atoms][128 words], box {128, atomsK, 1}
   CUtensorMap sfb;    // same for B, box {128, atomsK, atomsN}
@@ -102,7 +116,7 @@ template <Format F, uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 block_scaled_pair_gemm_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* __restrict__ c,
                               uint32_t m, uint32_t n, uint32_t k_stages, float alpha,
-                              uint32_t* __restrict__ status) {
+                              uint32_t* __restrict__ status, const Gather gather) {
   using L = Layout<F, BN, STAGES, ACC_STAGES>;
   using T = FormatTraits<F>;
   extern __shared__ uint8_t dynamic_shared[];
@@ -269,6 +283,7 @@ block_scaled_pair_gemm_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* 
     // ---------------------------------------------------------------------- epilogue
     const uint32_t quarter = warp % 4u;
     const bool vector_stores = (n % 8u) == 0u;
+    uint8_t* staging = shared + L::kStagingOffset + quarter * 4096u;
     uint32_t acc_stage = 0, acc_phase = 0;
     for (uint32_t tile = pair; tile < tiles; tile += pairs) {
       const uint32_t m0 = (tile % tiles_m) * 2u * kBlockM + rank * kBlockM;
@@ -291,28 +306,58 @@ block_scaled_pair_gemm_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* 
           }
         }
         const uint32_t column = n0 + chunk * 32u;
-        if (row < m && column < n) {
-          __nv_bfloat16* destination = c + static_cast<size_t>(row) * n + column;
-          if (vector_stores && column + 32u <= n) {
+        if (vector_stores) {
+          // A lane owns one accumulator row, so storing from registers would scatter 16-byte
+          // pieces over 32 rows. The warp instead transposes 64 columns through shared memory
+          // (16-byte pieces XOR-swizzled by row: conflict-free both ways) and writes whole
+          // 128-byte row segments, eight lanes to a row. Over NVLink that is the difference
+          // between 16-byte and 128-byte write packets.
 #pragma unroll
-            for (uint32_t part = 0; part < 4u; ++part) {
-              uint32_t packed[4];
+          for (uint32_t part = 0; part < 4u; ++part) {
+            uint32_t words[4];
 #pragma unroll
-              for (uint32_t pair_index = 0; pair_index < 4u; ++pair_index) {
-                const __nv_bfloat162 two = __floats2bfloat162_rn(
-                    __uint_as_float(values[part * 8u + pair_index * 2u]) * alpha,
-                    __uint_as_float(values[part * 8u + pair_index * 2u + 1u]) * alpha);
-                packed[pair_index] = *reinterpret_cast<const uint32_t*>(&two);
-              }
-              reinterpret_cast<uint4*>(destination)[part] =
-                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            for (uint32_t pair_index = 0; pair_index < 4u; ++pair_index) {
+              const __nv_bfloat162 two = __floats2bfloat162_rn(
+                  __uint_as_float(values[part * 8u + pair_index * 2u]) * alpha,
+                  __uint_as_float(values[part * 8u + pair_index * 2u + 1u]) * alpha);
+              words[pair_index] = *reinterpret_cast<const uint32_t*>(&two);
             }
-          } else {
+            const uint32_t piece = (chunk & 1u) * 4u + part;
+            *reinterpret_cast<uint4*>(staging + lane * 128u + ((piece ^ (lane & 7u)) * 16u)) =
+                make_uint4(words[0], words[1], words[2], words[3]);
+          }
+          if ((chunk & 1u) != 0u) {
+            __syncwarp();
+            const uint32_t piece = lane % 8u;
+            const uint32_t piece_column = column - 32u + piece * 8u;
 #pragma unroll
-            for (uint32_t item = 0; item < 32u; ++item) {
-              if (column + item < n) {
-                destination[item] = __float2bfloat16_rn(__uint_as_float(values[item]) * alpha);
+            for (uint32_t step = 0; step < 8u; ++step) {
+              const uint32_t local_row = step * 4u + lane / 8u;
+              const uint4 packed = *reinterpret_cast<const uint4*>(
+                  staging + local_row * 128u + ((piece ^ (local_row & 7u)) * 16u));
+              const uint32_t global_row = m0 + quarter * 32u + local_row;
+              if (global_row < m && piece_column < n) {
+                if (gather.count != 0u) {
+                  // Fused all-gather: the same bytes go to every GPU's full-width output.
+                  const size_t offset = static_cast<size_t>(global_row) * gather.row_stride +
+                                        gather.column_offset + piece_column;
+                  for (uint32_t target = 0; target < gather.count; ++target) {
+                    *reinterpret_cast<uint4*>(gather.outputs[target] + offset) = packed;
+                  }
+                } else {
+                  *reinterpret_cast<uint4*>(c + static_cast<size_t>(global_row) * n + piece_column) =
+                      packed;
+                }
               }
+            }
+            __syncwarp();
+          }
+        } else if (row < m && column < n) {
+          __nv_bfloat16* destination = c + static_cast<size_t>(row) * n + column;
+#pragma unroll
+          for (uint32_t item = 0; item < 32u; ++item) {
+            if (column + item < n) {
+              destination[item] = __float2bfloat16_rn(__uint_as_float(values[item]) * alpha);
             }
           }
         }
@@ -384,7 +429,8 @@ int encode_maps(Maps* maps, const Problem& problem, uint32_t block_n, const void
 }
 
 template <Format F, uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
-int launch(const Problem& problem, const Maps& maps, void* c, float alpha) {
+int launch(const Problem& problem, const Maps& maps, void* c, float alpha,
+           const Gather& gather = Gather{}) {
   using L = Layout<F, BN, STAGES, ACC_STAGES>;
   using T = FormatTraits<F>;
   auto function = block_scaled_pair_gemm_kernel<F, BN, STAGES, ACC_STAGES>;
@@ -424,7 +470,8 @@ int launch(const Problem& problem, const Maps& maps, void* c, float alpha) {
   if (tiles < pairs) pairs = tiles;
   const uint32_t k_stages = (problem.k + T::kElementsPerStage - 1u) / T::kElementsPerStage;
   function<<<2u * pairs, kThreads, L::kDynamicBytes, problem.stream>>>(
-      maps, static_cast<__nv_bfloat16*>(c), problem.m, problem.n, k_stages, alpha, problem.status);
+      maps, static_cast<__nv_bfloat16*>(c), problem.m, problem.n, k_stages, alpha, problem.status,
+      gather);
   return static_cast<int>(cudaPeekAtLastError());
 }
 

@@ -376,7 +376,8 @@ uint32_t choose_pair_block_n(int m, int n, int k, int sm_count) {
 }
 
 int execute_pair(Plan* plan, const void* a, const void* a_scales, const void* b,
-                 const void* b_scales, void* c) {
+                 const void* b_scales, void* c,
+                 const pair_gemm::Gather& gather = pair_gemm::Gather{}) {
   using pair_gemm::Format;
   pair_gemm::Problem problem{static_cast<uint32_t>(plan->m), static_cast<uint32_t>(plan->n),
                              static_cast<uint32_t>(plan->k), plan->device, plan->sm_count,
@@ -393,11 +394,14 @@ int execute_pair(Plan* plan, const void* a, const void* a_scales, const void* b,
   }
   switch (plan->block_n) {
     case 128u:
-      return pair_gemm::launch<Format::kMxFp8, 128u, 8u, 2u>(problem, plan->pair_maps, c, 1.0f);
+      return pair_gemm::launch<Format::kMxFp8, 128u, 8u, 2u>(problem, plan->pair_maps, c, 1.0f,
+                                                             gather);
     case 192u:
-      return pair_gemm::launch<Format::kMxFp8, 192u, 7u, 2u>(problem, plan->pair_maps, c, 1.0f);
+      return pair_gemm::launch<Format::kMxFp8, 192u, 7u, 2u>(problem, plan->pair_maps, c, 1.0f,
+                                                             gather);
     default:
-      return pair_gemm::launch<Format::kMxFp8, 256u, 6u, 1u>(problem, plan->pair_maps, c, 1.0f);
+      return pair_gemm::launch<Format::kMxFp8, 256u, 6u, 1u>(problem, plan->pair_maps, c, 1.0f,
+                                                             gather);
   }
 }
 
@@ -475,6 +479,41 @@ extern "C" int mircuda_mxfp8_tc_execute(void* raw, void* stream, const void* a,
     case 192u: return launch<192u, 5u, 2u>(plan, a_scales, b_scales, c);
     default: return launch<256u, 4u, 1u>(plan, a_scales, b_scales, c);
   }
+}
+
+extern "C" int mircuda_b200_mxfp8_tc_execute_gather(void* raw, void* stream, const void* a,
+                                                    const void* a_scales, const void* b,
+                                                    const void* b_scales, void* const* outputs,
+                                                    int output_count, int row_stride,
+                                                    int column_offset) {
+  using namespace mircuda_b200;
+  using namespace mircuda_b200::mxfp8_gemm;
+  if (raw == nullptr || stream == nullptr || a == nullptr || a_scales == nullptr ||
+      b == nullptr || b_scales == nullptr || outputs == nullptr || output_count <= 0 ||
+      output_count > 8 || row_stride <= 0 || column_offset < 0) {
+    return -1;
+  }
+  auto* plan = static_cast<Plan*>(raw);
+  if (static_cast<cudaStream_t>(stream) != plan->stream) return -1;
+  if (*static_cast<volatile uint32_t*>(plan->status) != 0u) return -3;
+  // The fused path lives in the CTA-pair kernel and stores 16-byte vectors.
+  if (!plan->pair || plan->n % 8 != 0 || row_stride % 8 != 0 || column_offset % 8 != 0 ||
+      column_offset + plan->n > row_stride) {
+    return -1;
+  }
+  if (((reinterpret_cast<uintptr_t>(a) | reinterpret_cast<uintptr_t>(b) |
+        reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u) != 0u) {
+    return -1;
+  }
+  pair_gemm::Gather gather{};
+  for (int index = 0; index < output_count; ++index) {
+    if (outputs[index] == nullptr || (reinterpret_cast<uintptr_t>(outputs[index]) & 15u) != 0u) return -1;
+    gather.outputs[index] = static_cast<__nv_bfloat16*>(outputs[index]);
+  }
+  gather.count = static_cast<uint32_t>(output_count);
+  gather.row_stride = static_cast<uint32_t>(row_stride);
+  gather.column_offset = static_cast<uint32_t>(column_offset);
+  return execute_pair(plan, a, a_scales, b, b_scales, outputs[0], gather);
 }
 
 extern "C" void mircuda_mxfp8_tc_destroy(void* raw) {

@@ -1,0 +1,58 @@
+"""Column-sharded linears across the GPUs of one box with the all-gather fused into the GEMM.
+
+Each rank owns a contiguous block of weight rows (`sharding.column_shard`), quantizes the
+replicated activations itself, and its GEMM epilogue stores every output tile straight into
+the full-width output buffer of every rank over NVLink (`mircuda_b200_mxfp8_tc_execute_gather`).
+The full-width buffers live in symmetric memory (`torch.distributed._symmetric_memory`), which
+is only used to obtain the peers' device pointers and a stream-ordered cross-GPU barrier.
+The reference has no multi-GPU path; the partitioning follows its operand layouts.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+import torch.distributed as dist
+
+from . import _lib
+from .plans import NativeError, StreamMismatch
+
+
+class SymmetricOutput:
+    """A [rows, columns] bf16 buffer with the same address layout on every rank."""
+
+    def __init__(self, rows: int, columns: int, device: torch.device, group=None):
+        import torch.distributed._symmetric_memory as symmetric_memory
+
+        self.rows, self.columns = rows, columns
+        self.group = group if group is not None else dist.group.WORLD
+        self.local = symmetric_memory.empty(rows * columns, dtype=torch.bfloat16, device=device)
+        self.handle = symmetric_memory.rendezvous(self.local, self.group)
+        self.world = dist.get_world_size(self.group)
+        pointers = [int(pointer) for pointer in self.handle.buffer_ptrs]
+        if len(pointers) != self.world:
+            raise RuntimeError("symmetric memory returned an unexpected number of peers")
+        self.pointers = (ctypes.c_void_p * self.world)(*pointers)
+
+    def barrier(self) -> None:
+        """Stream-ordered barrier over all ranks: after it, every rank's stores have landed."""
+        self.handle.barrier(channel=0)
+
+    def matrix(self) -> torch.Tensor:
+        return self.local.view(self.rows, self.columns)
+
+
+def execute_gather(plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
+                   output: SymmetricOutput, column_offset: int) -> None:
+    """Run `plan` (a BlockScaledMxFp8Plan over this rank's shard) and scatter its output
+    columns into every rank's `output` at `column_offset`."""
+    if stream.cuda_stream != plan._stream.cuda_stream:
+        raise StreamMismatch()
+    status = _lib.load().mircuda_b200_mxfp8_tc_execute_gather(
+        plan._raw, ctypes.c_void_p(stream.cuda_stream), ctypes.c_void_p(a.data_ptr()),
+        ctypes.c_void_p(a_scales.data_ptr()), ctypes.c_void_p(b.data_ptr()),
+        ctypes.c_void_p(b_scales.data_ptr()),
+        ctypes.cast(output.pointers, ctypes.POINTER(ctypes.c_void_p)), output.world,
+        output.columns, column_offset)
+    if status != 0:
+        raise NativeError(int(status))

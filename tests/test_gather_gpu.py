@@ -1,0 +1,66 @@
+"""Fused GEMM + all-gather over NVLink peer stores: two ranks, each owning half of the weight
+rows, must both end up with the full output, equal to the single-GPU result. Needs 2 GPUs
+(skipped otherwise); ranks run as child processes with NVLS off and plain peer stores."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _worker(rank, world, port, results):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import oracle
+        from helpers import bf16_bits
+        from mircuda_b200 import gather, plans, sharding
+        m, n, k = 512, 1024, 512
+        generator = torch.Generator().manual_seed(11)
+        x = torch.randn(m, k, generator=generator).to(torch.bfloat16).cuda()
+        w = (torch.randn(n, k, generator=generator) * 0.05).to(torch.bfloat16).cuda()
+        begin, end = sharding.column_shard(n, world, rank)
+        stream = torch.cuda.Stream()
+        a_codes = torch.empty(m * k, dtype=torch.uint8, device="cuda")
+        a_scales = torch.zeros(plans.scale_bytes(m, k // 32), dtype=torch.uint8, device="cuda")
+        b_codes = torch.empty((end - begin) * k, dtype=torch.uint8, device="cuda")
+        b_scales = torch.zeros(plans.scale_bytes(end - begin, k // 32), dtype=torch.uint8, device="cuda")
+        output = gather.SymmetricOutput(m, n, torch.device("cuda", rank))
+        output.local.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        plan = plans.BlockScaledMxFp8Plan(stream, plans.BlockScaledMxFp8Spec(m, end - begin, k))
+        with torch.cuda.stream(stream):
+            plans.mxfp8_quantize_bf16(stream, x, a_codes, a_scales)
+            plans.mxfp8_quantize_bf16(stream, w[begin:end].contiguous(), b_codes, b_scales)
+            gather.execute_gather(plan, stream, a_codes, a_scales, b_codes, b_scales, output, begin)
+            output.barrier()
+        stream.synchronize()
+        full_codes, full_scales = oracle.mxfp8_quantize(bf16_bits(w))
+        x_codes, x_scales = oracle.mxfp8_quantize(bf16_bits(x))
+        expected = oracle.mxfp8_gemm(x_codes, x_scales, full_codes, full_scales)
+        actual = bf16_bits(output.matrix())
+        stats = oracle.compare_bf16(actual, expected)
+        results[rank] = (not np.isnan(oracle.bf16_to_f32(actual)).any()
+                         and stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3)
+        dist.barrier()
+    finally:
+        dist.destroy_process_group()
+
+
+def test_fused_gather_two_ranks():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker, args=(2, port, results), nprocs=2, join=True)
+    assert dict(results) == {0: True, 1: True}
