@@ -23,6 +23,7 @@
 #include <new>
 
 #include "fp4_codec.cuh"
+#include "ptx.cuh"
 #include "layout.cuh"
 
 namespace mircuda_b200 {
@@ -137,7 +138,7 @@ fp4_vector_kernel(const uint8_t* __restrict__ input, const uint8_t* __restrict__
   if (slices == 1) return;
 
   // Last-arriving slice of this row tile reduces in slice order. No CTA waits on another.
-  __threadfence();
+  ptx::fence_acq_rel_gpu();
   __syncthreads();
   if (threadIdx.x == 0) {
     const unsigned int arrived = atomicAdd(&counters[row_tile], 1u);
@@ -146,7 +147,7 @@ fp4_vector_kernel(const uint8_t* __restrict__ input, const uint8_t* __restrict__
   }
   __syncthreads();
   if (!last_arrival) return;
-  __threadfence();
+  ptx::fence_acq_rel_gpu();
   if (threadIdx.x < kTileRows) {
     const int row = row_tile * kTileRows + threadIdx.x;
     float total = 0.0f;

@@ -20,6 +20,7 @@
 #include <cstdint>
 
 #include "fp4_codec.cuh"
+#include "ptx.cuh"
 
 namespace mircuda_b200 {
 namespace marlin_dense {
@@ -209,7 +210,7 @@ marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
   }
   if (slices == 1) return;
 
-  __threadfence();
+  ptx::fence_acq_rel_gpu();
   __syncthreads();
   if (threadIdx.x == 0) {
     const int arrived = atomicAdd(&locks[tile_n], 1);
@@ -218,7 +219,7 @@ marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
   }
   __syncthreads();
   if (!last_arrival) return;
-  __threadfence();
+  ptx::fence_acq_rel_gpu();
   for (int index = threadIdx.x; index < kTileN * kRows; index += kThreads) {
     const int n_local = index / kRows;
     const int row = index % kRows;

@@ -66,6 +66,14 @@ __device__ __forceinline__ bool mbarrier_try_wait(uint64_t* barrier, uint32_t pa
   return done != 0;
 }
 
+// Release/acquire fence at device scope. `__threadfence()` is the sequentially consistent
+// fence, which the hardware orders globally: hundreds of CTAs issuing it at the same moment
+// (the end of a split-K kernel) were measured to queue for 10 us and more. The hand-overs in
+// this library only need release/acquire ordering around an atomic counter.
+__device__ __forceinline__ void fence_acq_rel_gpu() {
+  asm volatile("fence.acq_rel.gpu;" ::: "memory");
+}
+
 __device__ __forceinline__ uint64_t global_timer_ns() {
   uint64_t now;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));

@@ -112,8 +112,13 @@ def test_fp4_vector_random(cuda_stream, n, k):
 
 # ------------------------------------------------------------------ bf16 x NVFP4 skinny GEMM
 
-@pytest.mark.parametrize("m", [1, 4, 8, 3])
-@pytest.mark.parametrize("n,k", [(4096, 4096), (200, 448), (129, 64), (6144, 1024)])
+@pytest.mark.parametrize("m,n,k", [
+    (m, n, k) for n, k in [(4096, 4096), (200, 448), (129, 64), (6144, 1024)] for m in [1, 4, 8, 3]
+] + [
+    # Shapes whose row tiles are shared between CTAs in every way: a CTA's share of the
+    # units starts and ends inside tiles, and covers whole tiles in between.
+    (8, 24576, 4096), (1, 24576, 4096), (8, 4096, 12288), (2, 12160, 2112),
+])
 def test_nvfp4_vector_random(cuda_stream, m, n, k):
     from mircuda_b200 import plans
     w, ws = random_fp4(n, k, 21)
