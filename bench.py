@@ -56,29 +56,43 @@ def measured_peaks() -> dict:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons through NVML while the timed region runs
+    (read-only queries, one every few milliseconds; `nvidia-smi` would take ~100 ms a call)."""
 
-    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
 
     def __init__(self, index: int):
         self.index = index
-        self.samples: list[list[str]] = []
+        self.clocks: list[int] = []
+        self.maximum = None
+        self.reasons: set[str] = set()
         self._stop = threading.Event()
         self._thread = threading.Thread(target=self._run, daemon=True)
 
     def _run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = self.index
+            if visible:
+                entry = visible.split(",")[self.index].strip()
+                index = int(entry) if entry.isdigit() else self.index
+            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.maximum = int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            return
         while not self._stop.is_set():
             try:
-                out = subprocess.run(
-                    ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.QUERY}",
-                     "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5)
-                if out.returncode == 0 and out.stdout.strip():
-                    self.samples.append([field.strip() for field in out.stdout.strip().split(",")])
+                self.clocks.append(int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
+                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.1)
+            self._stop.wait(0.004)
 
     def __enter__(self):
         self._thread.start()
@@ -89,19 +103,12 @@ class ClockSampler:
         self._thread.join(timeout=10)
 
     def summary(self) -> dict:
-        clocks = [int(s[0]) for s in self.samples if s and s[0].isdigit()]
-        maxima = [int(s[1]) for s in self.samples if len(s) > 1 and s[1].isdigit()]
-        reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for sample in self.samples:
-            for name, field in zip(names, sample[3:7]):
-                if field.lower().startswith("active"):
-                    reasons.add(name)
         return {
-            "sm_mhz": statistics.median(clocks) if clocks else None,
-            "sm_max_mhz": max(maxima) if maxima else None,
-            "reasons": sorted(reasons),
-            "samples": len(clocks),
+            "sm_mhz": statistics.median(self.clocks) if self.clocks else None,
+            "sm_min_mhz": min(self.clocks) if self.clocks else None,
+            "sm_max_mhz": self.maximum,
+            "reasons": sorted(self.reasons),
+            "samples": len(self.clocks),
         }
 
 
@@ -383,7 +390,12 @@ def run_gpu(args) -> None:
             },
             "roofline": {
                 "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak, "traffic": None, "kernel": "mxfp8_gemm_kernel",
+                "frac": achieved / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of the gate_up launch from the ncu
+                # capture summarised under profiles/ (algorithmic 322.5 MB; 33 MB of C were still
+                # dirty in L2 when the kernel ended). Not measured by this run.
+                "traffic": 289.6e6, "traffic_launch": "gate_up (M=4096, N=24576, K=4096)",
+                "kernel": "block_scaled_pair_gemm_kernel",
                 "peak_source": peak_note, "frac_of_nominal_fp8_4500": achieved / 4500.0,
                 "per_layer_tflops": {
                     name: 2.0 * TOKENS * next(l for l in layers if l["name"] == name)["local_n"]
@@ -407,7 +419,7 @@ def main() -> None:
     global SHAPES
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=20)
+    parser.add_argument("--steps", type=int, default=200)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")

@@ -158,6 +158,45 @@ int mircuda_variable_grouped_bf16_execute(void* plan, void* stream, const void* 
                                           const unsigned int* offsets, void* output, float beta);
 void mircuda_variable_grouped_bf16_destroy(void* plan);
 
+/* ------------------------------------------------------- grouped NVFP4 GEMMs (MoE) ----
+ * For each group g with matrix j = indices[g] (a group whose j >= matrices is skipped):
+ *   C[off_g + r, :] = bf16(alphas[j] * A[off_g + r, :] . B_j^T),  r < min(rows[g], max_m)
+ * A [capacity, k/2] and B [matrices, n, k/2] hold E2M1 pairs (even k low); scales are
+ * swizzled UE4M3 bytes per 16 K-elements: B's per matrix with stride
+ * ceil(n/128)*128 * (k/16) bytes, A's per group starting at 128-row tile
+ * scale_offsets[g] / 128. All routing arrays are device u32 that the host never reads.
+ * k % 64 == 0. Replace sys/native/variable_grouped_fp4_sm120.cu:178-222 and the paired
+ * variant, declared in sys/native/variable_grouped_fp4_sm120.cuh:99-122. */
+int mircuda_variable_grouped_fp4_create(int groups, int matrices, int max_m, int n, int k,
+                                        void* stream, void** output);
+int mircuda_variable_grouped_fp4_execute(void* plan, void* stream, const void* a,
+                                         const void* a_scales, const void* b,
+                                         const void* b_scales, const void* alphas,
+                                         const unsigned int* indices, const unsigned int* rows,
+                                         const unsigned int* offsets,
+                                         const unsigned int* scale_offsets, void* c);
+void mircuda_variable_grouped_fp4_destroy(void* plan);
+/* Two such problems (left, right) that share indices / rows / offsets / scale_offsets. */
+int mircuda_paired_variable_grouped_fp4_create(int groups, int matrices, int max_m, int n, int k,
+                                               void* stream, void** output);
+int mircuda_paired_variable_grouped_fp4_execute(
+    void* plan, void* stream, const void* left_a, const void* left_a_scales, const void* left_b,
+    const void* left_b_scales, const void* left_alphas, const void* right_a,
+    const void* right_a_scales, const void* right_b, const void* right_b_scales,
+    const void* right_alphas, const unsigned int* indices, const unsigned int* rows,
+    const unsigned int* offsets, const unsigned int* scale_offsets, void* left_c, void* right_c);
+void mircuda_paired_variable_grouped_fp4_destroy(void* plan);
+/* Fixed m rows per group (decode): group g multiplies A rows [g*m, g*m + m) (rows [0, m) of
+ * the single input when broadcast_input) by matrix selected[g] into C rows [g*m, g*m + m);
+ * A scales per input group with stride ceil(m/128)*128 * (k/16) bytes. Replaces
+ * sys/native/grouped_fp4_sm120.cu:145-207, declared in grouped_fp4_sm120.cuh:98-107. */
+int mircuda_grouped_fp4_create(int groups, int experts, int m, int n, int k,
+                               bool broadcast_input, void* stream, void** output);
+int mircuda_grouped_fp4_execute(void* plan, void* stream, const void* a, const void* a_scales,
+                                const void* b, const void* b_scales, const void* alphas,
+                                const unsigned int* selected, void* c);
+void mircuda_grouped_fp4_destroy(void* plan);
+
 /* ------------------------------------------------- Marlin-layout W4A16: preparation ----
  * One-time layout conversions and per-step route bucketing; stateless, integer, bit-exact.
  * Replace sys/native/marlin/repack.cu:271-end, declared in

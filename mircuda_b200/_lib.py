@@ -58,6 +58,15 @@ SIGNATURES.update({
     "mircuda_marlin_prepare_moe_routes": (_i, [_vp] * 8 + [_i, _i, _i]),
     "mircuda_marlin_nvfp4_dense_execute": (_i, [_vp] * 7 + [_i, _i, _i, _i, _vp, _b]),
     "mircuda_b200_mxfp8_tc_execute_gather": (_i, [_vp] * 6 + [_vpp, _i, _i, _i]),
+    "mircuda_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
+    "mircuda_variable_grouped_fp4_execute": (_i, [_vp] * 12),
+    "mircuda_variable_grouped_fp4_destroy": (None, [_vp]),
+    "mircuda_paired_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
+    "mircuda_paired_variable_grouped_fp4_execute": (_i, [_vp] * 18),
+    "mircuda_paired_variable_grouped_fp4_destroy": (None, [_vp]),
+    "mircuda_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _b, _vp, _vpp]),
+    "mircuda_grouped_fp4_execute": (_i, [_vp] * 9),
+    "mircuda_grouped_fp4_destroy": (None, [_vp]),
 })
 
 _handle = None

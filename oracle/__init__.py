@@ -360,6 +360,64 @@ def variable_grouped_bf16(a, weights, rows, offsets, c, max_rows: int, n: int, k
 
 # ------------------------------------------------------------------------------- metrics
 
+def variable_grouped_fp4(a, a_scales, b, b_scales, alphas, indices, rows, offsets, scale_offsets,
+                         c_bits, matrices: int, max_rows: int, n: int, k: int) -> np.ndarray:
+    """Variable-row grouped NVFP4 product (sys/native/variable_grouped_fp4_sm120.cu:31-62 for
+    the operand addressing; the arithmetic is CUTLASS's block-scaled MMA: exact E2M1 x UE4M3
+    products, fp32 accumulation, alpha, bf16 round). `c_bits` [capacity, n] is returned with
+    each group's rows replaced; a group whose index is out of range leaves its rows alone."""
+    a = _c(a, np.uint8).reshape(-1, k // 2)
+    b = _c(b, np.uint8).reshape(matrices, n, k // 2)
+    a_scales = _c(a_scales, np.uint8)
+    b_scales = _c(b_scales, np.uint8).reshape(matrices, -1)
+    output = np.array(c_bits, dtype=np.uint16).reshape(-1, n).copy()
+    atom_row_bytes = (k // 64) * 512
+    for group in range(len(indices)):
+        matrix = int(indices[group])
+        if matrix >= matrices:
+            continue
+        count = min(int(rows[group]), max_rows)
+        if count == 0:
+            continue
+        first = int(offsets[group])
+        scale_begin = (int(scale_offsets[group]) // 128) * atom_row_bytes
+        group_scales = a_scales[scale_begin:scale_begin + fp4_scale_bytes(count, k)]
+        left = nvfp4_dequantize(a[first:first + count], group_scales, k)
+        right = nvfp4_dequantize(b[matrix], b_scales[matrix], k)
+        product = (left @ right.T).astype(np.float32) * np.float32(alphas[matrix])
+        output[first:first + count] = f32_to_bf16(product.astype(np.float32))
+    return output
+
+
+def indexed_grouped_fp4(a, a_scales, b, b_scales, alphas, selected, c_bits, experts: int, m: int,
+                        n: int, k: int, broadcast_input: bool) -> np.ndarray:
+    """Fixed-m grouped NVFP4 product (sys/native/grouped_fp4_sm120.cu:29-57): group g reads
+    input group g (0 when broadcast), matrix selected[g], writes C rows [g*m, g*m + m)."""
+    groups = len(selected)
+    stride_rows = (m + 127) // 128 * 128
+    inputs = 1 if broadcast_input else groups
+    source = np.arange(groups) * 0 if broadcast_input else np.arange(groups)
+    padded = np.zeros((groups * m, k // 2), dtype=np.uint8)
+    a = _c(a, np.uint8).reshape(inputs, m, k // 2)
+    for group in range(groups):
+        padded[group * m:(group + 1) * m] = a[source[group]]
+    # Re-express as the variable problem: A rows copied per group, scales addressed per input.
+    output = np.array(c_bits, dtype=np.uint16).reshape(groups * m, n).copy()
+    a_scales = _c(a_scales, np.uint8).reshape(inputs, -1)
+    b = _c(b, np.uint8).reshape(experts, n, k // 2)
+    b_scales = _c(b_scales, np.uint8).reshape(experts, -1)
+    for group in range(groups):
+        expert = int(selected[group])
+        if expert >= experts:
+            continue
+        left = nvfp4_dequantize(padded[group * m:(group + 1) * m], a_scales[source[group]], k)
+        right = nvfp4_dequantize(b[expert], b_scales[expert], k)
+        product = (left @ right.T).astype(np.float32) * np.float32(alphas[expert])
+        output[group * m:(group + 1) * m] = f32_to_bf16(product.astype(np.float32))
+    del stride_rows
+    return output
+
+
 def compare_bf16(actual_bits, expected_bits) -> dict:
     """max|d|/max|ref| and relative Frobenius error between two bf16 bit arrays."""
     actual = bf16_to_f32(np.asarray(actual_bits).reshape(-1)).astype(np.float64)

@@ -196,3 +196,37 @@ def test_nvfp4_quantizer_spec_round_trip():
     codes, scales, global_scale = oracle.nvfp4_quantize(ones)
     assert np.isclose(global_scale, 1.0 / 2688.0)
     assert (codes == 0x77).all() and scales[oracle.fp4_scale_offsets(1, 64)].tolist() == [[0x7E] * 4]
+
+
+def test_variable_grouped_fp4_golden_rows():
+    """tests/cutlass/grouped/fp4.rs:38-87: both executions of the reference's variable-row test."""
+    n = k = 128
+    weights = np.full((3, n, k // 2), 0x22, np.uint8)
+    weights[0] = 0
+    bank_scales = np.full(3 * oracle.fp4_scale_bytes(n, k), 0x38, np.uint8)
+    a = np.full((6, k // 2), 0x22, np.uint8)
+    a_scales = np.full(4 * (k // 64) * 512, 0x38, np.uint8)
+    ones = np.full((6, n), 0x3F80, np.uint16)
+    first = oracle.variable_grouped_fp4(a, a_scales, weights, bank_scales, [1.0, 0.5, 0.25], [1, 0, 2, 1],
+                                        [3, 0, 2, 1], [0, 3, 3, 5], [0, 128, 128, 256], ones, 3, 4, n, k)
+    assert oracle.bf16_to_f32(first)[:, 0].tolist() == [64.0, 64.0, 64.0, 32.0, 32.0, 64.0]
+    second = oracle.variable_grouped_fp4(a, a_scales, weights, bank_scales, [1.0, 0.5, 0.25],
+                                         [1, 0, 2, 1], [0, 1, 1, 4], [0, 0, 1, 2], [0, 0, 128, 256],
+                                         first, 3, 4, n, k)
+    assert oracle.bf16_to_f32(second)[:, 0].tolist() == [0.0, 32.0, 64.0, 64.0, 64.0, 64.0]
+    assert (second == second[:, :1]).all()
+
+
+def test_indexed_grouped_fp4_golden_rows():
+    """tests/cutlass/grouped/fp4.rs:173-217 with broadcast input (run_case(2, 2, true))."""
+    n = k = 128
+    matrices = 33
+    weights = np.full((matrices, n, k // 2), 0x22, np.uint8)
+    weights[0] = 0
+    bank_scales = np.full(matrices * oracle.fp4_scale_bytes(n, k), 0x38, np.uint8)
+    alphas = [0.5 if matrix % 2 == 0 else 1.0 for matrix in range(matrices)]
+    a = np.full((2, k // 2), 0x22, np.uint8)
+    a_scales = np.full(oracle.fp4_scale_bytes(2, k), 0x38, np.uint8)
+    out = oracle.indexed_grouped_fp4(a, a_scales, weights, bank_scales, alphas, [0, 1],
+                                     np.full((4, n), 0x3F80, np.uint16), matrices, 2, n, k, True)
+    assert oracle.bf16_to_f32(out)[:, 0].tolist() == [0.0, 0.0, 128.0, 128.0]
