@@ -157,6 +157,19 @@ int mircuda_variable_grouped_bf16_execute(void* plan, void* stream, const void* 
                                           const void* weights, const unsigned int* rows,
                                           const unsigned int* offsets, void* output, float beta);
 void mircuda_variable_grouped_bf16_destroy(void* plan);
+/* The same product with the weight matrix of group g picked by indices[g] out of a bank
+ * W [matrices, n, k] (groups with an index >= matrices are skipped): expert-parallel MoE
+ * receives one group per (source GPU, local expert). NEW: the reference's bf16 grouped plan
+ * has no index array (its NVFP4 one does); plans are destroyed with
+ * mircuda_variable_grouped_bf16_destroy. */
+int mircuda_b200_variable_grouped_bf16_create_indexed(int groups, int matrices, int max_rows,
+                                                      int n, int k, void* stream, void** output);
+int mircuda_b200_variable_grouped_bf16_execute_indexed(void* plan, void* stream, const void* input,
+                                                       const void* weights,
+                                                       const unsigned int* indices,
+                                                       const unsigned int* rows,
+                                                       const unsigned int* offsets, void* output,
+                                                       float beta);
 
 /* ------------------------------------------------------- grouped NVFP4 GEMMs (MoE) ----
  * For each group g with matrix j = indices[g] (a group whose j >= matrices is skipped):
@@ -196,6 +209,57 @@ int mircuda_grouped_fp4_execute(void* plan, void* stream, const void* a, const v
                                 const void* b, const void* b_scales, const void* alphas,
                                 const unsigned int* selected, void* c);
 void mircuda_grouped_fp4_destroy(void* plan);
+
+/* ----------------------------------------------- MoE row helpers around the grouped GEMMs ----
+ * NEW (callers' side of the path; the reference has no counterpart). bf16 rows, columns % 8 == 0,
+ * 16-byte aligned buffers, all index arrays device i32 that the host never reads.
+ *   scatter_rows: destination[destination_index[i], :] = source[source_index[i], :] for i < count
+ *                 (a negative source index writes zeros, a negative destination skips the item)
+ *   swiglu:       output[r, j] = silu(input[r, j]) * input[r, intermediate + j], input [rows, 2*intermediate];
+ *                 when row_bound is not null only the first min(rows, *row_bound) rows (device u32)
+ *   combine_rows: output[t, :] = sum_j weights[t*top_k + j] * rows[index[t*top_k + j], :] (fp32 sums;
+ *                 a negative index drops the term) */
+int mircuda_b200_moe_scatter_rows_bf16(const void* source, const int* source_index,
+                                       const int* destination_index, void* destination,
+                                       uint32_t count, uint32_t columns, void* stream);
+int mircuda_b200_moe_swiglu_bf16(const void* input, void* output, uint32_t rows,
+                                 const unsigned int* row_bound, uint32_t intermediate,
+                                 void* stream);
+int mircuda_b200_moe_combine_rows_bf16(const void* rows, const int* index, const float* weights,
+                                       void* output, uint32_t tokens, uint32_t top_k,
+                                       uint32_t columns, void* stream);
+/* Received per-group row counts [blocks * per_block] -> the rows[] / offsets[] arrays of the
+ * grouped plans: group g of block s starts at s * block_rows + the `align`-rounded counts of
+ * the groups before it in the block (align 128 keeps NVFP4 scale tiles per group). */
+int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* rows, unsigned int* offsets,
+                                   uint32_t blocks, uint32_t per_block, uint32_t block_rows,
+                                   uint32_t align, void* stream);
+
+/* Expert parallelism over NVLink peer memory (NEW; no reference counterpart). Experts are
+ * sharded contiguously (experts / world per GPU); an owner stores each expert's rows from all
+ * sources contiguously, sources in rank order. all_counts [world][experts] holds every rank's
+ * rows per expert (exchanged by the caller). expert_layout writes base_for_me[e] = row on e's
+ * owner where this rank's rows for e start, and rows[] / offsets[] of this rank's own experts
+ * for the grouped plans (and their total in *received_rows when not null). dispatch_rows copies row source_index[i] of `source` to row
+ * base_for_me[sorted_expert[i]] + position[i] of the owner's receive buffer
+ * (receive_buffers[owner], peer-mapped pointers; world <= 8) and records that row in
+ * remote_row[i]. collect_rows sums, for every token, weights[t, j] * (row remote_row[slot[t, j]]
+ * of the owner's result buffer). The caller orders these launches against the peers with its
+ * own barriers; no kernel here waits for another GPU. */
+int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
+                                   uint32_t experts, int* base_for_me, unsigned int* rows,
+                                   unsigned int* offsets, unsigned int* received_rows,
+                                   void* stream);
+int mircuda_b200_moe_dispatch_rows_bf16(const void* source, const int* source_index,
+                                        const int* sorted_expert, const int* position,
+                                        const int* base_for_me, void* const* receive_buffers,
+                                        uint32_t world, int* remote_row, uint32_t count,
+                                        uint32_t local_experts, uint32_t columns, void* stream);
+int mircuda_b200_moe_collect_rows_bf16(void* const* result_buffers, uint32_t world, const int* slot,
+                                       const int* sorted_expert, const int* remote_row,
+                                       const float* weights, void* output, uint32_t tokens,
+                                       uint32_t top_k, uint32_t local_experts, uint32_t columns,
+                                       void* stream);
 
 /* ------------------------------------------------- Marlin-layout W4A16: preparation ----
  * One-time layout conversions and per-step route bucketing; stateless, integer, bit-exact.

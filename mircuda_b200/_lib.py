@@ -58,6 +58,15 @@ SIGNATURES.update({
     "mircuda_marlin_prepare_moe_routes": (_i, [_vp] * 8 + [_i, _i, _i]),
     "mircuda_marlin_nvfp4_dense_execute": (_i, [_vp] * 7 + [_i, _i, _i, _i, _vp, _b]),
     "mircuda_b200_mxfp8_tc_execute_gather": (_i, [_vp] * 6 + [_vpp, _i, _i, _i]),
+    "mircuda_b200_variable_grouped_bf16_create_indexed": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
+    "mircuda_b200_variable_grouped_bf16_execute_indexed": (_i, [_vp] * 8 + [_f]),
+    "mircuda_b200_moe_scatter_rows_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
+    "mircuda_b200_moe_swiglu_bf16": (_i, [_vp, _vp, _u32, _vp, _u32, _vp]),
+    "mircuda_b200_moe_combine_rows_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
+    "mircuda_b200_moe_group_offsets": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "mircuda_b200_moe_expert_layout": (_i, [_vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "mircuda_b200_moe_dispatch_rows_bf16": (_i, [_vp] * 5 + [_vpp, _u32, _vp, _u32, _u32, _u32, _vp]),
+    "mircuda_b200_moe_collect_rows_bf16": (_i, [_vpp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
     "mircuda_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_variable_grouped_fp4_execute": (_i, [_vp] * 12),
     "mircuda_variable_grouped_fp4_destroy": (None, [_vp]),

@@ -1,0 +1,153 @@
+"""Grouped MoE benchmark: Qwen3-30B-A3B-shaped feed-forward (128 experts, top-8, hidden 2048,
+expert intermediate 768, 4096 tokens) as bf16 and as NVFP4, experts sharded over the GPUs.
+
+    python -m mircuda_b200.bench_moe [--mode bf16|nvfp4|both] [--steps K] [--warmup W]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        -m mircuda_b200.bench_moe --mode bf16
+
+Inputs are synthetic and seeded (seed 5000 + index): activations N(0,1), expert weights
+N(0,0.02), router logits N(0,1) -> softmax -> top-8 -> renormalised. The total token count is
+fixed (strong scaling): each of N ranks routes 4096/N tokens and owns 128/N experts. A step is
+the whole layer of `mircuda_b200.moe` (count exchange, dispatch of the routed rows to the
+experts' owners, two grouped GEMMs with SwiGLU between them, weighted collection of the
+results); the router's output is prepared once, outside the timed region. One JSON line per
+mode: `value` = 2*assignments*(gate_up + down) flop of all ranks over the step time (max over
+ranks, CUDA events); `gemm` = the same flop over the summed durations of the two grouped GEMM
+launches on rank 0 (the grouped kernel alone); the bytes a rank moves over NVLink each way are
+reported beside them.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+import torch.distributed as dist
+
+from . import moe
+
+EXPERTS, TOP_K, HIDDEN, INTERMEDIATE, TOKENS = 128, 8, 2048, 768, 4096
+
+
+def main() -> None:
+    parser = argparse.ArgumentParser()
+    parser.add_argument("--mode", default="both", choices=["bf16", "nvfp4", "both"])
+    parser.add_argument("--steps", type=int, default=50)
+    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--transport", default="peer", choices=["peer", "nccl"],
+                        help="peer: this library's dispatch/collect kernels over NVLink peer memory; "
+                             "nccl: all_to_all_single of padded blocks")
+    args = parser.parse_args()
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    stream = torch.cuda.Stream()
+    local_tokens, local_experts = TOKENS // world, EXPERTS // world
+
+    with torch.cuda.stream(stream):
+        generator = torch.Generator(device=device).manual_seed(5000)
+        # Every rank draws the full token batch and router so that the shards agree; the expert
+        # banks are drawn per expert from their own seeds and only the local ones are kept.
+        x_all = torch.randn(TOKENS, HIDDEN, generator=generator, device=device).to(torch.bfloat16)
+        logits = torch.randn(TOKENS, EXPERTS, generator=generator, device=device)
+        x = x_all[rank * local_tokens:(rank + 1) * local_tokens].contiguous()
+        gate_up = torch.empty(local_experts, 2 * INTERMEDIATE, HIDDEN, dtype=torch.bfloat16, device=device)
+        down = torch.empty(local_experts, HIDDEN, INTERMEDIATE, dtype=torch.bfloat16, device=device)
+        for index in range(local_experts):
+            expert = rank * local_experts + index
+            local_generator = torch.Generator(device=device).manual_seed(5001 + expert)
+            gate_up[index] = (torch.randn(2 * INTERMEDIATE, HIDDEN, generator=local_generator, device=device) * 0.02).to(torch.bfloat16)
+            down[index] = (torch.randn(HIDDEN, INTERMEDIATE, generator=local_generator, device=device) * 0.02).to(torch.bfloat16)
+        chosen, weights = moe.route(logits[rank * local_tokens:(rank + 1) * local_tokens], TOP_K)
+    stream.synchronize()
+
+    modes = ["bf16", "nvfp4"] if args.mode == "both" else [args.mode]
+    for mode in modes:
+        nvfp4 = mode == "nvfp4"
+        if nvfp4 and world > 1:
+            if rank == 0:
+                print(json.dumps({"metric": "moe_grouped_gemm_tflops", "mode": mode, "n_gpus": world,
+                                  "unavailable": "NVFP4 expert parallelism not built yet"}), flush=True)
+            continue
+        align = 128 if nvfp4 else 1
+        dispatch = moe.plan_dispatch(chosen, EXPERTS, world, None, align)
+        largest = torch.tensor([dispatch.largest_block], device=device)
+        if world > 1:
+            dist.all_reduce(largest, op=dist.ReduceOp.MAX)
+        capacity = (int(largest.item()) + 127) // 128 * 128
+        dispatch = moe.plan_dispatch(chosen, EXPERTS, world, capacity, align)
+        peer = args.transport == "peer" and not nvfp4
+        if peer:
+            # Rows this rank will receive = everyone's counts for its experts (set-up time read).
+            totals = dispatch.counts.clone()
+            if world > 1:
+                dist.all_reduce(totals)
+            received = totals.view(world, local_experts).sum(dim=1).max()
+            capacity = (int(received.item()) + 127) // 128 * 128
+        bank = moe.ExpertWeights(stream, gate_up, down, nvfp4)
+        layer = moe.ExpertParallelMoe(stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, local_tokens,
+                                      capacity, bank, transport=args.transport)
+
+        def barrier():
+            stream.synchronize()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+
+        for _ in range(args.warmup):
+            layer.forward(x, dispatch, weights)
+        barrier()
+        layer.gemm_events = []
+        begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        begin.record(stream)
+        for _ in range(args.steps):
+            layer.forward(x, dispatch, weights)
+        end.record(stream)
+        barrier()
+        elapsed_ms = begin.elapsed_time(end)
+        if world > 1:
+            tensor = torch.tensor([elapsed_ms], device=device)
+            dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
+            elapsed_ms = float(tensor.item())
+        ms_per_step = elapsed_ms / args.steps
+        assignments = TOKENS * TOP_K
+        flops = {"gate_up": 2.0 * assignments * 2 * INTERMEDIATE * HIDDEN,
+                 "down": 2.0 * assignments * HIDDEN * INTERMEDIATE}
+        per_kernel = {}
+        for name, start, stop in layer.gemm_events:
+            per_kernel.setdefault(name, []).append(start.elapsed_time(stop))
+        # Rank 0's launches cover 1/world of the flop (experts and rows are balanced on average).
+        gemm_ms = {name: sum(times) / len(times) for name, times in per_kernel.items()}
+        line = {
+            "metric": "moe_grouped_gemm_tflops", "mode": mode, "n_gpus": world,
+            "transport": "peer" if peer else ("nccl" if world > 1 else "local"), "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "value": sum(flops.values()) / (ms_per_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+            "scaling": "strong", "data": "synthetic",
+            "gemm": {name: {"ms": gemm_ms[name],
+                            "tflops_per_gpu": flops[name] / world / (gemm_ms[name] * 1e-3) / 1e12}
+                     for name in gemm_ms},
+            "gemm_tflops_all_gpus": sum(flops.values()) / (sum(gemm_ms.values()) * 1e-3) / 1e12,
+            "config": {"workload": "qwen3-30b-a3b moe feed-forward", "experts": EXPERTS, "top_k": TOP_K,
+                       "hidden": HIDDEN, "intermediate": INTERMEDIATE, "tokens": TOKENS,
+                       "capacity_rows": capacity,
+                       "remote_bytes_per_rank_each_way":
+                           (world - 1) * (TOKENS * TOP_K // world // world if peer else capacity) * HIDDEN * 2},
+        }
+        if rank == 0:
+            print(json.dumps(line), flush=True)
+        layer.close()
+        del layer, bank
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -58,8 +58,10 @@ struct MapSet {
 // tile_starts[g] = number of tiles in groups before g (tiles = row tiles x column tiles);
 // tile_starts[groups] = total. One block; a serial carry across 1024-wide chunks.
 __global__ void __launch_bounds__(1024)
-grouped_bf16_setup_kernel(const unsigned int* __restrict__ rows, uint32_t groups,
-                          uint32_t max_rows, uint32_t tiles_n, uint32_t* __restrict__ tile_starts) {
+grouped_bf16_setup_kernel(const unsigned int* __restrict__ rows,
+                          const unsigned int* __restrict__ indices, uint32_t matrices,
+                          uint32_t groups, uint32_t max_rows, uint32_t tiles_n,
+                          uint32_t* __restrict__ tile_starts) {
   __shared__ uint32_t warp_totals[32];
   __shared__ uint32_t carry;
   if (threadIdx.x == 0) carry = 0u;
@@ -68,7 +70,9 @@ grouped_bf16_setup_kernel(const unsigned int* __restrict__ rows, uint32_t groups
     const uint32_t group = base + threadIdx.x;
     uint32_t count = 0u;
     if (group < groups) {
-      const uint32_t row_count = min(rows[group], max_rows);
+      // A group whose matrix index is out of range gets no tiles (it is skipped).
+      const bool routed = indices == nullptr || indices[group] < matrices;
+      const uint32_t row_count = routed ? min(rows[group], max_rows) : 0u;
       count = ((row_count + kBlockM - 1u) / kBlockM) * tiles_n;
     }
     uint32_t inclusive = count;
@@ -134,6 +138,7 @@ template <uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __restrict__ rows,
                     const unsigned int* __restrict__ offsets,
+                    const unsigned int* __restrict__ indices,
                     const uint32_t* __restrict__ tile_starts, __nv_bfloat16* __restrict__ c,
                     uint32_t groups, uint32_t max_rows, uint32_t n, uint32_t k, float beta,
                     uint32_t* __restrict__ status) {
@@ -186,6 +191,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
       bool running = true;
       for (uint32_t index = blockIdx.x; running && index < tiles; index += gridDim.x) {
         const Tile tile = locate(index, tile_starts, rows, offsets, groups, max_rows, BN);
+        const uint32_t matrix = indices == nullptr ? tile.group : __ldg(indices + tile.group);
         for (uint32_t kt = 0; kt < k_tiles; ++kt) {
           if (!ptx::mbarrier_wait(&empty[stage], phase ^ 1u, abort)) {
             running = false;
@@ -214,7 +220,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
             }
           }
           ptx::tma_load_3d(shared_b + stage * L::kBBytes, &maps.b, &full[stage], x,
-                           static_cast<int32_t>(tile.n0), static_cast<int32_t>(tile.group));
+                           static_cast<int32_t>(tile.n0), static_cast<int32_t>(matrix));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -343,6 +349,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
 
 struct Plan {
   int groups, max_rows, n, k;
+  int matrices;              // weight matrices in the bank (== groups without indices)
   int device, sm_count;
   uint32_t block_n;
   cudaStream_t stream;
@@ -369,7 +376,8 @@ inline int encode_3d_weight_map(CUtensorMap* map, const void* base, uint64_t gro
 }
 
 template <uint32_t BN, uint32_t STAGES, uint32_t ACC_STAGES>
-int launch(Plan* plan, const unsigned int* rows, const unsigned int* offsets, void* c, float beta) {
+int launch(Plan* plan, const unsigned int* rows, const unsigned int* offsets,
+           const unsigned int* indices, void* c, float beta) {
   using L = Layout<BN, STAGES, ACC_STAGES>;
   auto function = grouped_bf16_kernel<BN, STAGES, ACC_STAGES>;
   static thread_local int configured_device = -1;
@@ -380,7 +388,7 @@ int launch(Plan* plan, const unsigned int* rows, const unsigned int* offsets, vo
     configured_device = plan->device;
   }
   function<<<plan->sm_count, kThreads, L::kDynamicBytes, plan->stream>>>(
-      plan->maps, rows, offsets, plan->tile_starts, static_cast<__nv_bfloat16*>(c),
+      plan->maps, rows, offsets, indices, plan->tile_starts, static_cast<__nv_bfloat16*>(c),
       static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->max_rows),
       static_cast<uint32_t>(plan->n), static_cast<uint32_t>(plan->k), beta, plan->status);
   return static_cast<int>(cudaPeekAtLastError());
@@ -389,16 +397,18 @@ int launch(Plan* plan, const unsigned int* rows, const unsigned int* offsets, vo
 }  // namespace grouped_bf16
 }  // namespace mircuda_b200
 
-extern "C" int mircuda_variable_grouped_bf16_create(int groups, int max_rows, int n, int k,
-                                                    void* stream, void** output) {
-  using namespace mircuda_b200::grouped_bf16;
-  if (groups <= 0 || max_rows <= 0 || n <= 0 || k <= 0 || n % 8 != 0 || k % 8 != 0 ||
-      stream == nullptr || output == nullptr) {
+namespace mircuda_b200 {
+namespace grouped_bf16 {
+
+int create(int groups, int matrices, int max_rows, int n, int k, void* stream, void** output) {
+  if (groups <= 0 || matrices <= 0 || max_rows <= 0 || n <= 0 || k <= 0 || n % 8 != 0 ||
+      k % 8 != 0 || stream == nullptr || output == nullptr) {
     return -1;
   }
   auto* plan = new (std::nothrow) Plan{};
   if (plan == nullptr) return -2;
   plan->groups = groups;
+  plan->matrices = matrices;
   plan->max_rows = max_rows;
   plan->n = n;
   plan->k = k;
@@ -434,13 +444,9 @@ extern "C" int mircuda_variable_grouped_bf16_create(int groups, int max_rows, in
   return 0;
 }
 
-extern "C" int mircuda_variable_grouped_bf16_execute(void* raw, void* stream, const void* input,
-                                                     const void* weights,
-                                                     const unsigned int* rows,
-                                                     const unsigned int* offsets, void* output,
-                                                     float beta) {
-  using namespace mircuda_b200;
-  using namespace mircuda_b200::grouped_bf16;
+int execute(void* raw, void* stream, const void* input, const void* weights,
+            const unsigned int* indices, const unsigned int* rows, const unsigned int* offsets,
+            void* output, float beta) {
   if (raw == nullptr || stream == nullptr || input == nullptr || weights == nullptr ||
       rows == nullptr || offsets == nullptr || output == nullptr) {
     return -1;
@@ -464,19 +470,50 @@ extern "C" int mircuda_variable_grouped_bf16_execute(void* raw, void* stream, co
     plan->cached_input = input;
   }
   if (weights != plan->cached_weights) {
-    const int status = encode_3d_weight_map(&plan->maps.b, weights, plan->groups, plan->n, plan->k,
-                                            plan->block_n);
+    const int status = encode_3d_weight_map(&plan->maps.b, weights, plan->matrices, plan->n,
+                                            plan->k, plan->block_n);
     if (status != 0) return status;
     plan->cached_weights = weights;
   }
   const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
   grouped_bf16_setup_kernel<<<1, 1024, 0, cuda_stream>>>(
-      rows, static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->max_rows), tiles_n,
-      plan->tile_starts);
+      rows, indices, static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->groups),
+      static_cast<uint32_t>(plan->max_rows), tiles_n, plan->tile_starts);
   int status = static_cast<int>(cudaPeekAtLastError());
   if (status != 0) return status;
-  return plan->block_n == 128u ? launch<128u, 6u, 4u>(plan, rows, offsets, output, beta)
-                               : launch<256u, 4u, 2u>(plan, rows, offsets, output, beta);
+  return plan->block_n == 128u ? launch<128u, 6u, 4u>(plan, rows, offsets, indices, output, beta)
+                               : launch<256u, 4u, 2u>(plan, rows, offsets, indices, output, beta);
+}
+
+}  // namespace grouped_bf16
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_variable_grouped_bf16_create(int groups, int max_rows, int n, int k,
+                                                    void* stream, void** output) {
+  return mircuda_b200::grouped_bf16::create(groups, groups, max_rows, n, k, stream, output);
+}
+
+extern "C" int mircuda_variable_grouped_bf16_execute(void* raw, void* stream, const void* input,
+                                                     const void* weights,
+                                                     const unsigned int* rows,
+                                                     const unsigned int* offsets, void* output,
+                                                     float beta) {
+  return mircuda_b200::grouped_bf16::execute(raw, stream, input, weights, nullptr, rows, offsets,
+                                             output, beta);
+}
+
+extern "C" int mircuda_b200_variable_grouped_bf16_create_indexed(int groups, int matrices,
+                                                                 int max_rows, int n, int k,
+                                                                 void* stream, void** output) {
+  return mircuda_b200::grouped_bf16::create(groups, matrices, max_rows, n, k, stream, output);
+}
+
+extern "C" int mircuda_b200_variable_grouped_bf16_execute_indexed(
+    void* raw, void* stream, const void* input, const void* weights, const unsigned int* indices,
+    const unsigned int* rows, const unsigned int* offsets, void* output, float beta) {
+  if (indices == nullptr) return -1;
+  return mircuda_b200::grouped_bf16::execute(raw, stream, input, weights, indices, rows, offsets,
+                                             output, beta);
 }
 
 extern "C" void mircuda_variable_grouped_bf16_destroy(void* raw) {

@@ -420,9 +420,13 @@ class VariableGroupedBf16Spec:
     n: int
     k: int
     capacity_rows: int
+    # Not in the reference: size of a weight bank the groups index into (expert-parallel MoE
+    # has one group per (source GPU, local expert)); None = one matrix per group.
+    matrices: int | None = None
 
     def __post_init__(self):
-        values = (self.groups, self.max_rows, self.n, self.k, self.capacity_rows)
+        values = (self.groups, self.max_rows, self.n, self.k, self.capacity_rows,
+                  self.matrices if self.matrices is not None else 1)
         if any(v <= 0 for v in values) or self.n % 8 != 0 or self.k % 8 != 0:
             raise InvalidMatmulShape("invalid grouped bf16 shape")
         if max(values) > 2**32 - 1:
@@ -437,24 +441,41 @@ class VariableGroupedBf16Plan:
         self._lib = _lib.load()
         self.spec, self._stream = spec, stream
         raw = ctypes.c_void_p()
-        _check(self._lib.mircuda_variable_grouped_bf16_create(
-            spec.groups, spec.max_rows, spec.n, spec.k, _stream_handle(stream), ctypes.byref(raw)))
+        if spec.matrices is None:
+            _check(self._lib.mircuda_variable_grouped_bf16_create(
+                spec.groups, spec.max_rows, spec.n, spec.k, _stream_handle(stream),
+                ctypes.byref(raw)))
+        else:
+            _check(self._lib.mircuda_b200_variable_grouped_bf16_create_indexed(
+                spec.groups, spec.matrices, spec.max_rows, spec.n, spec.k, _stream_handle(stream),
+                ctypes.byref(raw)))
         self._raw = raw
 
-    def execute(self, stream, input, weights, rows, offsets, output, beta: float = 0.0):
+    def execute(self, stream, input, weights, rows, offsets, output, beta: float = 0.0,
+                indices=None):
         if stream.cuda_stream != self._stream.cuda_stream:
             raise StreamMismatch()
         s = self.spec
         _exact("input", s.capacity_rows * s.k, input)
-        _exact("weights", s.groups * s.n * s.k, weights)
+        _exact("weights", (s.matrices or s.groups) * s.n * s.k, weights)
         _exact("rows", s.groups, rows)
         _exact("offsets", s.groups, offsets)
         _exact("output", s.capacity_rows * s.n, output)
         words = (torch.int32, torch.uint32)
-        _check(self._lib.mircuda_variable_grouped_bf16_execute(
+        if s.matrices is None:
+            if indices is not None:
+                raise ValueError("indices need a spec with `matrices`")
+            _check(self._lib.mircuda_variable_grouped_bf16_execute(
+                self._raw, _stream_handle(stream), _device_pointer(input, _BF16),
+                _device_pointer(weights, _BF16), _device_pointer(rows, words),
+                _device_pointer(offsets, words), _device_pointer(output, _BF16), float(beta)))
+            return
+        _exact("indices", s.groups, indices)
+        _check(self._lib.mircuda_b200_variable_grouped_bf16_execute_indexed(
             self._raw, _stream_handle(stream), _device_pointer(input, _BF16),
-            _device_pointer(weights, _BF16), _device_pointer(rows, words),
-            _device_pointer(offsets, words), _device_pointer(output, _BF16), float(beta)))
+            _device_pointer(weights, _BF16), _device_pointer(indices, words),
+            _device_pointer(rows, words), _device_pointer(offsets, words),
+            _device_pointer(output, _BF16), float(beta)))
 
     def close(self):
         if getattr(self, "_raw", None):

@@ -96,3 +96,35 @@ def test_grouped_bf16_moe_shape_sample(cuda_stream):
                                                 np.zeros((capacity, n), np.uint16), capacity, n, k, 0.0)
         assert_close_bf16(bf16_bits(out), expected, f"moe sample attempt {attempt}")
     plan.close()
+
+
+def test_grouped_bf16_indexed_bank(cuda_stream):
+    """Groups pick their matrix out of a smaller bank through a device index array (one group
+    per (source GPU, local expert) in expert-parallel MoE); an out-of-range index skips the
+    group. Expected values come from the plain oracle on the gathered weights."""
+    from mircuda_b200 import plans
+    groups, matrices, n, k, max_rows = 10, 3, 264, 136, 200
+    rows = [5, 130, 0, 64, 200, 1, 33, 128, 90, 17]
+    indices = [2, 0, 1, 1, 2, 7, 0, 1, 2, 0]            # group 5 is out of range
+    offsets = np.concatenate([[0], np.cumsum(rows)[:-1]]).tolist()
+    capacity = sum(rows) + 4
+    a = seeded_bf16((capacity, k), 1.0, 6100)
+    bank = seeded_bf16((matrices * n, k), 0.05, 6101)
+    c = seeded_bf16((capacity, n), 1.0, 6102)
+    gathered = torch.cat([bank.view(matrices, n, k)[min(i, matrices - 1)] for i in indices])
+    effective_rows = [0 if i >= matrices else r for r, i in zip(rows, indices)]
+    expected = oracle.variable_grouped_bf16(bf16_bits(a), bf16_bits(gathered), effective_rows, offsets,
+                                            bf16_bits(c), max_rows, n, k, 0.0)
+    plan = plans.VariableGroupedBf16Plan(
+        cuda_stream, plans.VariableGroupedBf16Spec(groups, max_rows, n, k, capacity, matrices))
+    as_words = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    out = c.clone()
+    torch.cuda.synchronize()
+    plan.execute(cuda_stream, a.view(-1), bank.view(-1), as_words(rows), as_words(offsets),
+                 out.view(-1), 0.0, indices=as_words(indices))
+    cuda_stream.synchronize()
+    plan.close()
+    assert_close_bf16(bf16_bits(out).reshape(capacity, n), expected, "indexed grouped bf16")
+    begin = offsets[5]
+    assert (bf16_bits(out).reshape(capacity, n)[begin:begin + rows[5]] ==
+            bf16_bits(c).reshape(capacity, n)[begin:begin + rows[5]]).all()
