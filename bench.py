@@ -257,6 +257,11 @@ def run_gpu(args) -> None:
     stream.synchronize()
 
     gemm_events: list[tuple] = []
+    # MIRCUDA_B200_GATHER=multimem writes every piece once through the buffers' NVSwitch
+    # multicast address instead of once per rank. Measured at 4 GPUs it is 5 % slower than the
+    # per-rank stores (the receiving side, not this GPU's egress, is the limit), so it is opt-in.
+    use_multicast = os.environ.get("MIRCUDA_B200_GATHER", "peer") == "multimem"
+    multicast_active = bool(fused and use_multicast and all(layer["full"].multicast for layer in layers))
 
     def one_step(record: bool):
         for layer in layers:
@@ -269,7 +274,7 @@ def run_gpu(args) -> None:
             if fused:
                 gather.execute_gather(op.plan, stream, op.scratch.quantized_input,
                                       op.scratch.input_scales, layer["codes"], layer["scales"],
-                                      layer["full"], layer["begin"])
+                                      layer["full"], layer["begin"], use_multicast)
             else:
                 op.plan.execute(stream, op.scratch.quantized_input, op.scratch.input_scales,
                                 layer["codes"], layer["scales"], layer["out"])
@@ -344,7 +349,7 @@ def run_gpu(args) -> None:
                                               op.scratch.input_scales)
                     gather.execute_gather(op.plan, stream, op.scratch.quantized_input,
                                           op.scratch.input_scales, layer["codes"], layer["scales"],
-                                          layer["full"], layer["begin"])
+                                          layer["full"], layer["begin"], use_multicast)
                     layer["full"].barrier()
                     # Each rank reads back its own column block of the gathered result.
                     out_host.view(TOKENS, layer["local_n"]).copy_(
@@ -383,7 +388,9 @@ def run_gpu(args) -> None:
                 "workload": WORKLOAD, "tokens": TOKENS,
                 "shapes": {name: [n, k] for name, n, k in SHAPES},
                 "parallelism": (f"weight N column-sharded x{world}, all-gather fused into the GEMM "
-                                "epilogue (peer stores over NVLink)" if fused else
+                                "epilogue (" + ("multimem stores through NVSwitch multicast"
+                                                if multicast_active else "peer stores over NVLink") + ")"
+                                if fused else
                                 f"weight N column-sharded x{world}, NCCL all-gather of outputs"
                                 if distributed else "single GPU"),
                 "l2": "per-step operands (193 MB of weights + activations + 318 MB of outputs) exceed the 126 MB L2",

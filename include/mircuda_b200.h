@@ -63,12 +63,15 @@ void mircuda_mxfp8_tc_destroy(void* plan);
  * stores every tile into the full-width output [m, row_stride] of each of `output_count`
  * GPUs (<= 8, the caller's own buffer among them) at column `column_offset`, through
  * peer-mapped device pointers (CUDA IPC / symmetric memory), with plain stores over NVLink.
- * The caller orders the peers' reads after this launch (a cross-GPU barrier on the stream).
- * Needs m > 128 and n, row_stride, column_offset multiples of 8; -1 otherwise. */
+ * If `multicast_output` is not null it must be the NVSwitch multicast address of those same
+ * buffers; every piece is then written once with a multimem store and replicated by the
+ * switch. The caller orders the peers' reads after this launch (a cross-GPU barrier on the
+ * stream). Needs m > 128 and n, row_stride, column_offset multiples of 8; -1 otherwise. */
 int mircuda_b200_mxfp8_tc_execute_gather(void* plan, void* stream, const void* a,
                                          const void* a_scales, const void* b,
                                          const void* b_scales, void* const* outputs,
-                                         int output_count, int row_stride, int column_offset);
+                                         int output_count, int row_stride, int column_offset,
+                                         void* multicast_output);
 
 /* Weight-only MXFP8 (bf16 activations, row-major [n, k/32] E8M0 scales, weights as
  * little-endian u32 words), any token count. Replaces `mircuda_mxfp8_bf16` and

@@ -96,10 +96,16 @@ struct Layout {
 // Fused GEMM + all-gather for column-sharded linears: when `count` is non-zero the epilogue
 // does not write C[M, n] locally but stores every tile into the full-width output
 // [M, row_stride] of each of `count` GPUs (this GPU's own buffer among them) at column
-// `column_offset`, with ordinary stores through peer-mapped pointers. The transfer over
-// NVLink then overlaps the MMAs of the following tiles and no separate collective runs.
+// `column_offset`, with ordinary stores through peer-mapped pointers or, when the buffers are
+// bound to an NVSwitch multicast object, with one multimem store that the switch replicates.
+// The transfer over NVLink then overlaps the MMAs of the following tiles and no separate
+// collective runs.
 struct Gather {
   __nv_bfloat16* outputs[8];
+  // When not null: the multicast address of the same buffers (one NVSwitch multicast object
+  // bound on every GPU). A single multimem store then reaches all of them, so this GPU's
+  // NVLink egress is one copy of its shard instead of one per peer.
+  __nv_bfloat16* multicast;
   uint32_t count;
   uint32_t row_stride;
   uint32_t column_offset;
@@ -341,8 +347,15 @@ block_scaled_pair_gemm_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* 
                   // Fused all-gather: the same bytes go to every GPU's full-width output.
                   const size_t offset = static_cast<size_t>(global_row) * gather.row_stride +
                                         gather.column_offset + piece_column;
-                  for (uint32_t target = 0; target < gather.count; ++target) {
-                    *reinterpret_cast<uint4*>(gather.outputs[target] + offset) = packed;
+                  if (gather.multicast != nullptr) {
+                    asm volatile("multimem.st.weak.global.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(
+                                     gather.multicast + offset),
+                                 "r"(packed.x), "r"(packed.y), "r"(packed.z), "r"(packed.w)
+                                 : "memory");
+                  } else {
+                    for (uint32_t target = 0; target < gather.count; ++target) {
+                      *reinterpret_cast<uint4*>(gather.outputs[target] + offset) = packed;
+                    }
                   }
                 } else {
                   *reinterpret_cast<uint4*>(c + static_cast<size_t>(global_row) * n + piece_column) =

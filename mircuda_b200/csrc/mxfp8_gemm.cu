@@ -485,7 +485,7 @@ extern "C" int mircuda_b200_mxfp8_tc_execute_gather(void* raw, void* stream, con
                                                     const void* a_scales, const void* b,
                                                     const void* b_scales, void* const* outputs,
                                                     int output_count, int row_stride,
-                                                    int column_offset) {
+                                                    int column_offset, void* multicast_output) {
   using namespace mircuda_b200;
   using namespace mircuda_b200::mxfp8_gemm;
   if (raw == nullptr || stream == nullptr || a == nullptr || a_scales == nullptr ||
@@ -510,6 +510,7 @@ extern "C" int mircuda_b200_mxfp8_tc_execute_gather(void* raw, void* stream, con
     if (outputs[index] == nullptr || (reinterpret_cast<uintptr_t>(outputs[index]) & 15u) != 0u) return -1;
     gather.outputs[index] = static_cast<__nv_bfloat16*>(outputs[index]);
   }
+  gather.multicast = static_cast<__nv_bfloat16*>(multicast_output);
   gather.count = static_cast<uint32_t>(output_count);
   gather.row_stride = static_cast<uint32_t>(row_stride);
   gather.column_offset = static_cast<uint32_t>(column_offset);

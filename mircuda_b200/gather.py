@@ -33,6 +33,9 @@ class SymmetricOutput:
         if len(pointers) != self.world:
             raise RuntimeError("symmetric memory returned an unexpected number of peers")
         self.pointers = (ctypes.c_void_p * self.world)(*pointers)
+        # NVSwitch multicast address of the same buffers (0 when the fabric or the allocation
+        # has none): one multimem store to it reaches every rank's copy.
+        self.multicast = int(getattr(self.handle, "multicast_ptr", 0) or 0)
 
     def barrier(self) -> None:
         """Stream-ordered barrier over all ranks: after it, every rank's stores have landed."""
@@ -43,9 +46,10 @@ class SymmetricOutput:
 
 
 def execute_gather(plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
-                   output: SymmetricOutput, column_offset: int) -> None:
+                   output: SymmetricOutput, column_offset: int, multicast: bool = False) -> None:
     """Run `plan` (a BlockScaledMxFp8Plan over this rank's shard) and scatter its output
-    columns into every rank's `output` at `column_offset`."""
+    columns into every rank's `output` at `column_offset`: through the buffers' multicast
+    address when there is one and `multicast` is set, else with one store per rank."""
     if stream.cuda_stream != plan._stream.cuda_stream:
         raise StreamMismatch()
     status = _lib.load().mircuda_b200_mxfp8_tc_execute_gather(
@@ -53,6 +57,7 @@ def execute_gather(plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
         ctypes.c_void_p(a_scales.data_ptr()), ctypes.c_void_p(b.data_ptr()),
         ctypes.c_void_p(b_scales.data_ptr()),
         ctypes.cast(output.pointers, ctypes.POINTER(ctypes.c_void_p)), output.world,
-        output.columns, column_offset)
+        output.columns, column_offset,
+        ctypes.c_void_p(output.multicast if multicast and output.multicast else None))
     if status != 0:
         raise NativeError(int(status))
