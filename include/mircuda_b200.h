@@ -264,6 +264,30 @@ int mircuda_b200_moe_collect_rows_bf16(void* const* result_buffers, uint32_t wor
                                        uint32_t top_k, uint32_t local_experts, uint32_t columns,
                                        void* stream);
 
+/* ------------------------------------------------------------- dense f16 / bf16 GEMM ----
+ * C[m, n] = alpha * A[m, k] . B[n, k]^T + beta * C; input_type 0 = f16, 1 = bf16; output_type
+ * = input_type or 2 (f32). Any shape: k and n multiples of 8 run on tcgen05, others on a
+ * CUDA-core kernel. Replaces sys/native/dense_sm120.cu:130-184, declared in
+ * sys/src/platform/cutlass/dense/mod.rs:14-33. workspace_bytes is always 0. */
+int mircuda_dense_create(int input_type, int output_type, int m, int n, int k, void* stream,
+                         void** output);
+size_t mircuda_dense_workspace_bytes(const void* plan);
+int mircuda_dense_execute(void* plan, void* stream, const void* a, const void* b, void* c,
+                          float alpha, float beta);
+void mircuda_dense_destroy(void* plan);
+
+/* ------------------------------------------------ W4A16 with symmetric int4 weights ----
+ * NEW: the reference's W4A16 is the NVFP4/MXFP4 Marlin path; it has no int4 entry point.
+ * y[m, n] = f16(sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128]): x, y f16; weights [n, k/2]
+ * bytes, even k in the low nibble, q in 0..15; scales f16 [n, k/128]. k % 128 == 0,
+ * n % 8 == 0. m <= 16 streams the packed weights once (HBM-bound GEMV); larger m expands the
+ * weights into a plan-owned f16 workspace (workspace_bytes) and runs the dense GEMM. */
+int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void** output);
+size_t mircuda_b200_w4a16_workspace_bytes(const void* plan);
+int mircuda_b200_w4a16_execute(void* plan, void* stream, const void* input, const void* weight,
+                               const void* scales, void* output);
+void mircuda_b200_w4a16_destroy(void* plan);
+
 /* ------------------------------------------------- Marlin-layout W4A16: preparation ----
  * One-time layout conversions and per-step route bucketing; stateless, integer, bit-exact.
  * Replace sys/native/marlin/repack.cu:271-end, declared in

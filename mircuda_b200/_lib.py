@@ -67,6 +67,14 @@ SIGNATURES.update({
     "mircuda_b200_moe_expert_layout": (_i, [_vp, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
     "mircuda_b200_moe_dispatch_rows_bf16": (_i, [_vp] * 5 + [_vpp, _u32, _vp, _u32, _u32, _u32, _vp]),
     "mircuda_b200_moe_collect_rows_bf16": (_i, [_vpp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
+    "mircuda_dense_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
+    "mircuda_dense_workspace_bytes": (_sz, [_vp]),
+    "mircuda_dense_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _f]),
+    "mircuda_dense_destroy": (None, [_vp]),
+    "mircuda_b200_w4a16_create": (_i, [_i, _i, _i, _vp, _vpp]),
+    "mircuda_b200_w4a16_workspace_bytes": (_sz, [_vp]),
+    "mircuda_b200_w4a16_execute": (_i, [_vp] * 6),
+    "mircuda_b200_w4a16_destroy": (None, [_vp]),
     "mircuda_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_variable_grouped_fp4_execute": (_i, [_vp] * 12),
     "mircuda_variable_grouped_fp4_destroy": (None, [_vp]),

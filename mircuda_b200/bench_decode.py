@@ -1,6 +1,6 @@
 """Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
 
-    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin]
+    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16]
 
 Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
 examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
@@ -8,7 +8,8 @@ banks that their total exceeds 768 MiB (at least 8 banks), so no launch finds it
 the 126 MB L2; `cycles` back-to-back launches are timed between two CUDA events on the
 launching stream after a warm-up pass; the median of `repeats` timings is reported.
 Bytes counted per launch are the algorithmic ones: weights + scales + activations + outputs.
-Shapes: the four Qwen3-8B linears (N, K) at M in {1, 4, 8}. Prints one JSON line per op and
+Shapes: the four Qwen3-8B linears (N, K) at M in {1, 4, 8}; for the int4-g128 W4A16 op,
+K=4096 x N=14336 and K=14336 x N=4096 at M in {1, 16, 256} (TFLOP/s reported beside GB/s). Prints one JSON line per op and
 a final summary line.
 """
 from __future__ import annotations
@@ -139,15 +140,35 @@ def bench_marlin(stream, n, k, m, cycles, repeats):
     return seconds, n * k * 0.5625 + m * k * 2 + m * n * 2, banks
 
 
+W4A16_SHAPES = [("k4096_n14336", 14336, 4096), ("k14336_n4096", 4096, 14336)]
+
+
+def bench_w4a16(stream, n, k, m, cycles, repeats):
+    """int4-g128 weights, f16 activations (the Marlin-style W4A16 shapes of the benchmark)."""
+    from . import dense
+    banks = _banks(n * k // 2 + n * k // 128 * 2)
+    weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+    scales = [(torch.rand(n * k // 128, device="cuda") * 0.01 + 0.002).to(torch.float16)
+              for _ in range(banks)]
+    x = torch.randn(m * k, device="cuda").to(torch.float16)
+    out = torch.empty(m * n, dtype=torch.float16, device="cuda")
+    plan = dense.W4A16Plan(stream, dense.W4A16Spec(m, n, k))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute(stream, x, weights[i], scales[i], out),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, n * k * 0.5 + n * k / 128 * 2 + m * k * 2 + m * n * 2, banks
+
+
 def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None) -> dict:
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
     results = []
     for op in ops:
-        for name, n, k in SHAPES:
+        for name, n, k in (W4A16_SHAPES if op == "w4a16" else SHAPES):
             if shapes and name not in shapes:
                 continue
-            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1]):
+            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else [1]):
                 if tokens and m not in tokens:
                     continue
                 with torch.cuda.stream(stream):
@@ -157,12 +178,16 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                         seconds, byte_count, banks = bench_fp4(stream, n, k, cycles, repeats)
                     elif op == "dense":
                         seconds, byte_count, banks = bench_dense(stream, n, k, cycles, repeats)
+                    elif op == "w4a16":
+                        seconds, byte_count, banks = bench_w4a16(stream, n, k, m, cycles, repeats)
                     else:
                         seconds, byte_count, banks = bench_marlin(stream, n, k, m, cycles, repeats)
                 torch.cuda.empty_cache()
                 record = {"op": op, "shape": name, "n": n, "k": k, "m": m, "us": seconds * 1e6,
                           "gbs": byte_count / seconds / 1e9, "frac_of_measured_hbm":
                           byte_count / seconds / 1e9 / peak_gbs, "banks": banks}
+                if op == "w4a16":
+                    record["tflops"] = 2.0 * m * n * k / seconds / 1e12
                 results.append(record)
                 print(json.dumps(record), flush=True)
     return {"results": results}
@@ -172,7 +197,7 @@ def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--cycles", type=int, default=200)
     parser.add_argument("--repeats", type=int, default=5)
-    parser.add_argument("--ops", default="nvfp4,fp4,dense,marlin")
+    parser.add_argument("--ops", default="nvfp4,fp4,dense,marlin,w4a16")
     parser.add_argument("--peak-gbs", type=float, default=6551.4)
     parser.add_argument("--shapes", default="", help="subset of qkv,o,gate_up,down (profiling runs)")
     parser.add_argument("--tokens", default="", help="subset of 1,4,8 (profiling runs)")

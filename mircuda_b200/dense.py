@@ -1,0 +1,129 @@
+"""Host-side mirrors of the reference's dense GEMM plan (src/cutlass/dense.rs,
+sys/src/platform/cutlass/dense/mod.rs) and of the int4 W4A16 plan this library adds."""
+from __future__ import annotations
+
+import ctypes
+from dataclasses import dataclass
+
+import torch
+
+from . import _lib
+from .plans import (InvalidMatmulShape, StreamMismatch, _check, _device_pointer, _exact,
+                    _stream_handle)
+
+_TYPES = {torch.float16: 0, torch.bfloat16: 1, torch.float32: 2}
+
+
+@dataclass(frozen=True)
+class DenseMatmulSpec:
+    """``DenseMatmulSpec`` (sys/src/platform/cutlass/dense/mod.rs:55-62): C[m,n] = alpha A B^T + beta C."""
+    m: int
+    n: int
+    k: int
+    input_type: torch.dtype = torch.bfloat16
+    output_type: torch.dtype | None = None
+
+    def __post_init__(self):
+        if self.m <= 0 or self.n <= 0 or self.k <= 0:
+            raise InvalidMatmulShape("invalid dense shape")
+        if self.input_type not in (torch.float16, torch.bfloat16):
+            raise InvalidMatmulShape("inputs are f16 or bf16")
+        if self.output() not in (self.input_type, torch.float32):
+            raise InvalidMatmulShape("output is the input type or f32")
+
+    def output(self) -> torch.dtype:
+        return self.output_type or self.input_type
+
+
+class DenseMatmulPlan:
+    """``DenseMatmulPlan`` over ``mircuda_dense_*``."""
+
+    def __init__(self, stream, spec: DenseMatmulSpec):
+        self._lib = _lib.load()
+        self.spec, self._stream = spec, stream
+        raw = ctypes.c_void_p()
+        _check(self._lib.mircuda_dense_create(_TYPES[spec.input_type], _TYPES[spec.output()], spec.m,
+                                              spec.n, spec.k, _stream_handle(stream), ctypes.byref(raw)))
+        self._raw = raw
+
+    def execute(self, stream, a, b, c, alpha: float = 1.0, beta: float = 0.0) -> None:
+        if stream.cuda_stream != self._stream.cuda_stream:
+            raise StreamMismatch()
+        s = self.spec
+        _exact("A", s.m * s.k, a)
+        _exact("B", s.n * s.k, b)
+        _exact("C", s.m * s.n, c)
+        _check(self._lib.mircuda_dense_execute(
+            self._raw, _stream_handle(stream), _device_pointer(a, (s.input_type,)),
+            _device_pointer(b, (s.input_type,)), _device_pointer(c, (s.output(),)), float(alpha),
+            float(beta)))
+
+    def close(self) -> None:
+        if getattr(self, "_raw", None):
+            self._lib.mircuda_dense_destroy(self._raw)
+            self._raw = None
+
+    __del__ = close
+
+
+GROUP = 128
+
+
+def quantize_int4(weight: torch.Tensor):
+    """Symmetric int4 with zero point 8, one f16 scale = max|w| / 7 per 128 K-elements:
+    returns (packed codes u8 [n, k/2], even k in the low nibble; scales f16 [n, k/128])."""
+    n, k = weight.shape
+    if k % GROUP != 0:
+        raise InvalidMatmulShape("k must be a multiple of 128")
+    groups = weight.float().view(n, k // GROUP, GROUP)
+    scales = (groups.abs().amax(dim=-1) / 7.0).to(torch.float16)
+    safe = torch.where(scales == 0, torch.ones_like(scales), scales).float()
+    codes = torch.clamp(torch.round(groups / safe[..., None]) + 8, 0, 15).to(torch.uint8).view(n, k)
+    packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
+    return packed, scales.contiguous()
+
+
+@dataclass(frozen=True)
+class W4A16Spec:
+    m: int
+    n: int
+    k: int
+
+    def __post_init__(self):
+        if self.m <= 0 or self.n <= 0 or self.k <= 0 or self.k % GROUP != 0 or self.n % 8 != 0:
+            raise InvalidMatmulShape("invalid int4 W4A16 shape")
+
+
+class W4A16Plan:
+    """f16 activations x int4-g128 weights over ``mircuda_b200_w4a16_*`` (no reference plan)."""
+
+    def __init__(self, stream, spec: W4A16Spec):
+        self._lib = _lib.load()
+        self.spec, self._stream = spec, stream
+        raw = ctypes.c_void_p()
+        _check(self._lib.mircuda_b200_w4a16_create(spec.m, spec.n, spec.k, _stream_handle(stream),
+                                                   ctypes.byref(raw)))
+        self._raw = raw
+
+    def workspace_bytes(self) -> int:
+        return int(self._lib.mircuda_b200_w4a16_workspace_bytes(self._raw))
+
+    def execute(self, stream, input, weight, scales, output) -> None:
+        if stream.cuda_stream != self._stream.cuda_stream:
+            raise StreamMismatch()
+        s = self.spec
+        _exact("input", s.m * s.k, input)
+        _exact("weight", s.n * s.k // 2, weight)
+        _exact("scales", s.n * s.k // GROUP, scales)
+        _exact("output", s.m * s.n, output)
+        _check(self._lib.mircuda_b200_w4a16_execute(
+            self._raw, _stream_handle(stream), _device_pointer(input, (torch.float16,)),
+            _device_pointer(weight, (torch.uint8, torch.int8)), _device_pointer(scales, (torch.float16,)),
+            _device_pointer(output, (torch.float16,))))
+
+    def close(self) -> None:
+        if getattr(self, "_raw", None):
+            self._lib.mircuda_b200_w4a16_destroy(self._raw)
+            self._raw = None
+
+    __del__ = close

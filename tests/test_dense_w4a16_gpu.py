@@ -1,0 +1,121 @@
+"""GPU parity for the dense f16/bf16 GEMM (mircuda_dense_*) and the int4-g128 W4A16 op."""
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def assert_close(actual: torch.Tensor, expected: torch.Tensor, what: str):
+    actual, expected = actual.double().cpu(), expected.double().cpu()
+    assert torch.isfinite(actual).all(), what
+    scale = expected.abs().max().clamp_min(1e-30)
+    assert (actual - expected).abs().max() <= 1e-2 * scale, what
+    assert (actual - expected).norm() <= 5e-3 * expected.norm().clamp_min(1e-30), what
+
+
+def run_dense(stream, a, b, c, spec, alpha, beta):
+    from mircuda_b200 import dense
+    plan = dense.DenseMatmulPlan(stream, spec)
+    torch.cuda.synchronize()
+    plan.execute(stream, a.reshape(-1), b.reshape(-1), c.view(-1), alpha, beta)
+    stream.synchronize()
+    plan.close()
+    return c
+
+
+@pytest.mark.parametrize("m", [1, 128])
+def test_dense_bf16_golden(cuda_stream, m):
+    """tests/cutlass/dense/mod.rs:22-26 (run_bf16): ones x ones, N = K = 128 -> 128."""
+    from mircuda_b200 import dense
+    a = torch.ones(m, 128, dtype=torch.bfloat16, device="cuda")
+    b = torch.ones(128, 128, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(m, 128, dtype=torch.bfloat16, device="cuda")
+    run_dense(cuda_stream, a, b, c, dense.DenseMatmulSpec(m, 128, 128), 1.0, 0.0)
+    assert (c.float() == 128.0).all()
+
+
+def test_dense_bf16_wide_decode_golden(cuda_stream):
+    """tests/cutlass/dense/mod.rs:28-40: M = 1, N = 8192, K = 128."""
+    from mircuda_b200 import dense
+    a = torch.ones(1, 128, dtype=torch.bfloat16, device="cuda")
+    b = torch.ones(8192, 128, dtype=torch.bfloat16, device="cuda")
+    c = torch.zeros(1, 8192, dtype=torch.bfloat16, device="cuda")
+    run_dense(cuda_stream, a, b, c, dense.DenseMatmulSpec(1, 8192, 128), 1.0, 0.0)
+    assert (c.float() == 128.0).all()
+
+
+def test_dense_bf16_fp32_output_golden(cuda_stream):
+    """tests/cutlass/dense/mod.rs:42-58: the f32 result must not be rounded to bf16."""
+    from mircuda_b200 import dense
+    a = torch.full((1, 128), 0.1, dtype=torch.bfloat16, device="cuda")
+    b = torch.full((128, 128), 0.1, dtype=torch.bfloat16, device="cuda")
+    c = torch.full((1, 128), float("nan"), dtype=torch.float32, device="cuda")
+    run_dense(cuda_stream, a, b, c, dense.DenseMatmulSpec(1, 128, 128, torch.bfloat16, torch.float32), 1.0, 0.0)
+    assert torch.isfinite(c).all() and (c - c[0, 0]).abs().max() < 1.2e-7
+    assert abs(float(c[0, 0]) - float(c[0, 0].to(torch.bfloat16))) > 1.2e-7
+
+
+def test_dense_bf16_unaligned_golden(cuda_stream):
+    """tests/cutlass/dense/mod.rs:60-72: M=2, N=4, K=3, alpha = beta = 1 on ones -> 4."""
+    from mircuda_b200 import dense
+    a = torch.ones(2, 3, dtype=torch.bfloat16, device="cuda")
+    b = torch.ones(4, 3, dtype=torch.bfloat16, device="cuda")
+    c = torch.ones(2, 4, dtype=torch.bfloat16, device="cuda")
+    run_dense(cuda_stream, a, b, c, dense.DenseMatmulSpec(2, 4, 3), 1.0, 1.0)
+    assert (c.float() == 4.0).all()
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("m,n,k,alpha,beta", [(256, 512, 1024, 1.0, 0.0), (300, 328, 200, 0.5, 0.25),
+                                              (5, 1000, 64, 1.0, 0.0), (129, 264, 136, 1.0, 1.0)])
+def test_dense_random(cuda_stream, dtype, m, n, k, alpha, beta):
+    from mircuda_b200 import dense
+    generator = torch.Generator(device="cuda").manual_seed(8100 + m)
+    a = torch.randn(m, k, generator=generator, device="cuda").to(dtype)
+    b = (torch.randn(n, k, generator=generator, device="cuda") * 0.05).to(dtype)
+    c0 = torch.randn(m, n, generator=generator, device="cuda").to(dtype)
+    expected = alpha * (a.double() @ b.double().T) + beta * c0.double()
+    c = c0.clone()
+    run_dense(cuda_stream, a, b, c, dense.DenseMatmulSpec(m, n, k, dtype), alpha, beta)
+    assert_close(c, expected, f"dense {dtype} {m}x{n}x{k}")
+
+
+def w4a16_reference(x, packed, scales):
+    codes = torch.stack([packed & 15, packed >> 4], dim=-1).reshape(packed.shape[0], -1).double()
+    weights = (codes - 8.0) * scales.double().repeat_interleave(128, dim=1)
+    return x.double() @ weights.T
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (4, 1000, 512), (8, 200, 128), (16, 640, 2048),
+                                   (9, 4096, 4096), (256, 512, 1024), (40, 264, 384)])
+def test_w4a16_random(cuda_stream, m, n, k):
+    from mircuda_b200 import dense
+    generator = torch.Generator(device="cuda").manual_seed(8200 + m)
+    weight = torch.randn(n, k, generator=generator, device="cuda") * 0.02
+    packed, scales = dense.quantize_int4(weight)
+    x = torch.randn(m, k, generator=generator, device="cuda").to(torch.float16)
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    plan = dense.W4A16Plan(cuda_stream, dense.W4A16Spec(m, n, k))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        plan.execute(cuda_stream, x.view(-1), packed.view(-1), scales.view(-1), out.view(-1))
+    cuda_stream.synchronize()
+    plan.close()
+    assert_close(out, w4a16_reference(x, packed, scales), f"w4a16 {m}x{n}x{k}")
+
+
+def test_w4a16_nibble_order(cuda_stream):
+    """Only even-k codes differ from the zero point: exposes a swapped nibble order."""
+    from mircuda_b200 import dense
+    n, k = 128, 128
+    packed = torch.full((n, k // 2), 0x89, dtype=torch.uint8, device="cuda")   # even k: +1, odd k: 0
+    scales = torch.ones(n, 1, dtype=torch.float16, device="cuda")
+    x = torch.arange(k, dtype=torch.float32, device="cuda").to(torch.float16).view(1, k)
+    out = torch.zeros(1, n, dtype=torch.float16, device="cuda")
+    plan = dense.W4A16Plan(cuda_stream, dense.W4A16Spec(1, n, k))
+    torch.cuda.synchronize()
+    plan.execute(cuda_stream, x.view(-1), packed.view(-1), scales.view(-1), out.view(-1))
+    cuda_stream.synchronize()
+    plan.close()
+    assert (out.float() == float(sum(range(0, k, 2)))).all()
