@@ -264,6 +264,30 @@ int mircuda_b200_moe_collect_rows_bf16(void* const* result_buffers, uint32_t wor
                                        uint32_t top_k, uint32_t local_experts, uint32_t columns,
                                        void* stream);
 
+/* ------------------------------------------------- Marlin-layout W4A16: routed (MoE) ----
+ * For every assignment id = token * top_k + choice routed to expert e:
+ *   output[id, :] = bf16(input[id / top_k, :] . W_e^T * scale_e) (* routing[id] if multiply_routing)
+ * with weights / scales from the mircuda_marlin_* preparation entry points and routes from
+ * mircuda_marlin_prepare_moe_routes (block size 8 for thread_config 0-2, 64 for 3-5).
+ * `temporary`, `locks`, `atomic_reduce` are accepted for compatibility and not used (no K
+ * slicing). Replace sys/native/marlin/moe_kernel.cu:175-205 and mxfp4_moe_kernel.cu:145-171,
+ * declared in sys/src/platform/marlin/execute/mod.rs:32-53 and execute/mxfp4.rs:13-34.
+ * output_features % 64 == 0; input_features % 16 == 0 (32 for MXFP4). */
+int mircuda_marlin_nvfp4_moe_execute(void* stream, const void* input, const void* weight,
+                                     void* output, void* temporary, const void* scales,
+                                     const void* global_scales, const void* sorted,
+                                     const void* expert_ids, const void* padded,
+                                     const void* routing, int top_k, bool multiply_routing,
+                                     int tokens, int output_features, int input_features,
+                                     int thread_config, void* locks, bool atomic_reduce);
+int mircuda_marlin_mxfp4_moe_execute(void* stream, const void* input, const void* weight,
+                                     void* output, void* temporary, const void* scales,
+                                     const void* sorted, const void* expert_ids,
+                                     const void* padded, const void* routing, int top_k,
+                                     bool multiply_routing, int tokens, int output_features,
+                                     int input_features, int thread_config, void* locks,
+                                     bool atomic_reduce);
+
 /* ------------------------------------------------------------- dense f16 / bf16 GEMM ----
  * C[m, n] = alpha * A[m, k] . B[n, k]^T + beta * C; input_type 0 = f16, 1 = bf16; output_type
  * = input_type or 2 (f32). Any shape: k and n multiples of 8 run on tcgen05, others on a
