@@ -29,6 +29,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <new>
 
 #include "fp4_codec.cuh"
@@ -381,6 +382,11 @@ extern "C" int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* strea
   }
   *plan->status = 0u;
   plan->parts = parts_for(n, k, sm_count);
+  if (const char* forced = std::getenv("MIRCUDA_B200_NVFP4_PARTS")) {
+    const int value = std::atoi(forced);
+    const int stages = (k + kStageK - 1) / kStageK;
+    if ((value == 1 || value == 2 || value == 4 || value == 8) && value <= stages) plan->parts = value;
+  }
   *output = plan;
   return 0;
 }
