@@ -147,6 +147,12 @@ int mircuda_b200_nvfp4_global_scale(const void* input, size_t elements, void* gl
                                     void* stream);
 int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale, void* codes,
                                      void* scales, uint32_t rows, uint32_t k, void* stream);
+/* The same quantizer with the scales left row-major, [rows, k/16] bytes, for rows that are
+ * moved (dispatched to another GPU) before their final place and scale tile are known;
+ * mircuda_b200_mxfp8_swizzle_scales (a plain byte permutation) then builds the atoms. */
+int mircuda_b200_nvfp4_quantize_rows_bf16(const void* input, const void* global_scale,
+                                          void* codes, void* row_scales, uint32_t rows,
+                                          uint32_t k, void* stream);
 
 /* -------------------------------------------------- variable-row grouped bf16 GEMM ----
  * For each group g: C[off_g : off_g + min(rows_g, max_rows), :] = A[same rows] . W_g^T
@@ -240,7 +246,9 @@ int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* rows, unsign
 
 /* Expert parallelism over NVLink peer memory (NEW; no reference counterpart). Experts are
  * sharded contiguously (experts / world per GPU); an owner stores each expert's rows from all
- * sources contiguously, sources in rank order. all_counts [world][experts] holds every rank's
+ * sources contiguously, sources in rank order, every expert starting on a multiple of `align`
+ * rows (128 for NVFP4 activations). Rows are 2-byte units here: packed codes or scale bytes
+ * travel through the same kernels as `columns` = bytes / 2. all_counts [world][experts] holds every rank's
  * rows per expert (exchanged by the caller). expert_layout writes base_for_me[e] = row on e's
  * owner where this rank's rows for e start, and rows[] / offsets[] of this rank's own experts
  * for the grouped plans (and their total in *received_rows when not null). dispatch_rows copies row source_index[i] of `source` to row
@@ -250,9 +258,9 @@ int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* rows, unsign
  * of the owner's result buffer). The caller orders these launches against the peers with its
  * own barriers; no kernel here waits for another GPU. */
 int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
-                                   uint32_t experts, int* base_for_me, unsigned int* rows,
-                                   unsigned int* offsets, unsigned int* received_rows,
-                                   void* stream);
+                                   uint32_t experts, uint32_t align, int* base_for_me,
+                                   unsigned int* rows, unsigned int* offsets,
+                                   unsigned int* received_rows, void* stream);
 int mircuda_b200_moe_dispatch_rows_bf16(const void* source, const int* source_index,
                                         const int* sorted_expert, const int* position,
                                         const int* base_for_me, void* const* receive_buffers,

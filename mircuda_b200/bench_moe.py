@@ -38,6 +38,9 @@ def main() -> None:
     parser.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                         help="peer: this library's dispatch/collect kernels over NVLink peer memory; "
                              "nccl: all_to_all_single of padded blocks")
+    parser.add_argument("--graph", action="store_true",
+                        help="replay the step from a CUDA graph (no host launch cost; the grouped "
+                             "GEMMs are then not timed separately)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -69,10 +72,11 @@ def main() -> None:
     modes = ["bf16", "nvfp4"] if args.mode == "both" else [args.mode]
     for mode in modes:
         nvfp4 = mode == "nvfp4"
-        if nvfp4 and world > 1:
+        if nvfp4 and world > 1 and args.transport != "peer":
             if rank == 0:
                 print(json.dumps({"metric": "moe_grouped_gemm_tflops", "mode": mode, "n_gpus": world,
-                                  "unavailable": "NVFP4 expert parallelism not built yet"}), flush=True)
+                                  "unavailable": "NVFP4 expert parallelism uses the peer transport"}),
+                      flush=True)
             continue
         align = 128 if nvfp4 else 1
         dispatch = moe.plan_dispatch(chosen, EXPERTS, world, None, align)
@@ -81,17 +85,21 @@ def main() -> None:
             dist.all_reduce(largest, op=dist.ReduceOp.MAX)
         capacity = (int(largest.item()) + 127) // 128 * 128
         dispatch = moe.plan_dispatch(chosen, EXPERTS, world, capacity, align)
-        peer = args.transport == "peer" and not nvfp4
+        peer = args.transport == "peer"
         if peer:
-            # Rows this rank will receive = everyone's counts for its experts (set-up time read).
+            # Rows this rank will receive = everyone's counts for its experts, every expert
+            # rounded up to `align` rows (set-up time read).
             totals = dispatch.counts.clone()
             if world > 1:
                 dist.all_reduce(totals)
+            totals = (totals + align - 1) // align * align
             received = totals.view(world, local_experts).sum(dim=1).max()
             capacity = (int(received.item()) + 127) // 128 * 128
         bank = moe.ExpertWeights(stream, gate_up, down, nvfp4)
         layer = moe.ExpertParallelMoe(stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, local_tokens,
                                       capacity, bank, transport=args.transport)
+        if nvfp4:
+            layer.calibrate(x)
 
         def barrier():
             stream.synchronize()
@@ -103,12 +111,25 @@ def main() -> None:
         for _ in range(args.warmup):
             layer.forward(x, dispatch, weights)
         barrier()
-        layer.gemm_events = []
+        graph = None
+        if args.graph:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                layer.forward(x, dispatch, weights)
+            with torch.cuda.stream(stream):
+                graph.replay()
+            barrier()
+        else:
+            layer.gemm_events = []
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        begin.record(stream)
-        for _ in range(args.steps):
-            layer.forward(x, dispatch, weights)
-        end.record(stream)
+        with torch.cuda.stream(stream):
+            begin.record(stream)
+            for _ in range(args.steps):
+                if graph is not None:
+                    graph.replay()
+                else:
+                    layer.forward(x, dispatch, weights)
+            end.record(stream)
         barrier()
         elapsed_ms = begin.elapsed_time(end)
         if world > 1:
@@ -120,7 +141,7 @@ def main() -> None:
         flops = {"gate_up": 2.0 * assignments * 2 * INTERMEDIATE * HIDDEN,
                  "down": 2.0 * assignments * HIDDEN * INTERMEDIATE}
         per_kernel = {}
-        for name, start, stop in layer.gemm_events:
+        for name, start, stop in (layer.gemm_events or []):
             per_kernel.setdefault(name, []).append(start.elapsed_time(stop))
         # Rank 0's launches cover 1/world of the flop (experts and rows are balanced on average).
         gemm_ms = {name: sum(times) / len(times) for name, times in per_kernel.items()}
@@ -133,11 +154,16 @@ def main() -> None:
             "gemm": {name: {"ms": gemm_ms[name],
                             "tflops_per_gpu": flops[name] / world / (gemm_ms[name] * 1e-3) / 1e12}
                      for name in gemm_ms},
-            "gemm_tflops_all_gpus": sum(flops.values()) / (sum(gemm_ms.values()) * 1e-3) / 1e12,
+            "gemm_tflops_all_gpus": (sum(flops.values()) / (sum(gemm_ms.values()) * 1e-3) / 1e12
+                                     if gemm_ms else None),
+            "cuda_graph": bool(args.graph),
             "config": {"workload": "qwen3-30b-a3b moe feed-forward", "experts": EXPERTS, "top_k": TOP_K,
                        "hidden": HIDDEN, "intermediate": INTERMEDIATE, "tokens": TOKENS,
                        "capacity_rows": capacity,
-                       "remote_bytes_per_rank_each_way":
+                       "remote_bytes_per_rank_dispatch":
+                           (world - 1) * (TOKENS * TOP_K // world // world if peer else capacity)
+                           * (HIDDEN * 9 // 16 if nvfp4 else HIDDEN * 2),
+                       "remote_bytes_per_rank_collect":
                            (world - 1) * (TOKENS * TOP_K // world // world if peer else capacity) * HIDDEN * 2},
         }
         if rank == 0:

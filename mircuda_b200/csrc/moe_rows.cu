@@ -124,12 +124,13 @@ __global__ void moe_group_offsets_kernel(const int* __restrict__ counts, unsigne
 // Expert-parallel layout, one thread per global expert e (owner GPU = e / local_experts).
 // all_counts[s][e] = rows GPU s routes to expert e. Every owner stores an expert's rows from
 // all sources contiguously, sources in rank order, experts in index order:
-//   start[e]        = rows of the owner's experts before e
+//   start[e]        = rows of the owner's experts before e (each rounded up to `align` rows,
+//                     128 to keep NVFP4 scale tiles per expert)
 //   base_for_me[e]  = start[e] + rows of sources before `rank`  (where this rank's rows go)
 //   rows/offsets    = the grouped plans' arrays for this rank's own experts
 __global__ void moe_expert_layout_kernel(const int* __restrict__ all_counts, uint32_t world,
                                          uint32_t rank, uint32_t experts, uint32_t local_experts,
-                                         int* __restrict__ base_for_me, unsigned int* __restrict__ rows,
+                                         uint32_t align, int* __restrict__ base_for_me, unsigned int* __restrict__ rows,
                                          unsigned int* __restrict__ offsets,
                                          unsigned int* __restrict__ received_rows) {
   extern __shared__ uint32_t totals[];
@@ -147,13 +148,15 @@ __global__ void moe_expert_layout_kernel(const int* __restrict__ all_counts, uin
   if (expert >= experts) return;
   const uint32_t owner_first = expert / local_experts * local_experts;
   uint32_t start = 0u;
-  for (uint32_t other = owner_first; other < expert; ++other) start += totals[other];
+  for (uint32_t other = owner_first; other < expert; ++other) {
+    start += (totals[other] + align - 1u) / align * align;
+  }
   base_for_me[expert] = static_cast<int>(start + before_me);
   if (expert / local_experts == rank) {
     rows[expert - owner_first] = total;
     offsets[expert - owner_first] = start;
     if (expert - owner_first + 1u == local_experts && received_rows != nullptr) {
-      *received_rows = start + total;
+      *received_rows = start + (total + align - 1u) / align * align;
     }
   }
 }
@@ -298,17 +301,18 @@ extern "C" int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* r
 }
 
 extern "C" int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
-                                              uint32_t experts, int* base_for_me,
+                                              uint32_t experts, uint32_t align, int* base_for_me,
                                               unsigned int* rows, unsigned int* offsets,
                                               unsigned int* received_rows, void* stream) {
   using namespace mircuda_b200::moe_rows;
   if (all_counts == nullptr || base_for_me == nullptr || rows == nullptr || offsets == nullptr ||
       world == 0 || world > 8 || rank >= world || experts == 0 || experts > 1024 ||
-      experts % world != 0) {
+      experts % world != 0 || align == 0) {
     return -1;
   }
   moe_expert_layout_kernel<<<1, experts, experts * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
-      all_counts, world, rank, experts, experts / world, base_for_me, rows, offsets, received_rows);
+      all_counts, world, rank, experts, experts / world, align, base_for_me, rows, offsets,
+      received_rows);
   return static_cast<int>(cudaPeekAtLastError());
 }
 

@@ -68,6 +68,9 @@ __device__ __forceinline__ uint32_t encode_e2m1_pair(float low, float high) {
 }
 
 // One thread per 16-element block: two 16-byte loads, one 8-byte store, one scale byte.
+// ROW_MAJOR_SCALES: scales go to [rows, k/16] bytes instead of the swizzled atoms, so that
+// whole rows (codes and scales) can be moved to another place before the layout is fixed.
+template <bool ROW_MAJOR_SCALES>
 __global__ void __launch_bounds__(256)
 nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
                 uint2* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t rows,
@@ -101,7 +104,7 @@ nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__
   codes[block] = make_uint2(out[0], out[1]);
   const uint32_t row = static_cast<uint32_t>(block / blocks_per_row);
   const uint32_t column = static_cast<uint32_t>(block % blocks_per_row);
-  scales[scale_offset(row, column, blocks_per_row)] = scale_code;
+  scales[ROW_MAJOR_SCALES ? block : scale_offset(row, column, blocks_per_row)] = scale_code;
 }
 
 }  // namespace
@@ -131,10 +134,12 @@ extern "C" int mircuda_b200_nvfp4_global_scale(const void* input, size_t element
   return static_cast<int>(cudaPeekAtLastError());
 }
 
-extern "C" int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale,
-                                                void* codes, void* scales, uint32_t rows,
-                                                uint32_t k, void* stream) {
-  using namespace mircuda_b200;
+namespace mircuda_b200 {
+namespace {
+
+template <bool ROW_MAJOR_SCALES>
+int launch_quantize(const void* input, const void* global_scale, void* codes, void* scales,
+                    uint32_t rows, uint32_t k, void* stream) {
   if (input == nullptr || global_scale == nullptr || codes == nullptr || scales == nullptr ||
       stream == nullptr || rows == 0u || k == 0u || k % 64u != 0u) {
     return -1;
@@ -146,8 +151,24 @@ extern "C" int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* g
   const size_t blocks = static_cast<size_t>(rows) * (k / 16u);
   const size_t grid = (blocks + 255u) / 256u;
   if (grid > 0x7fffffffull) return -1;
-  nvfp4_quantize_kernel<<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
-      static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, k);
+  nvfp4_quantize_kernel<ROW_MAJOR_SCALES>
+      <<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+          static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
+          static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, k);
   return static_cast<int>(cudaPeekAtLastError());
+}
+
+}  // namespace
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_nvfp4_quantize_bf16(const void* input, const void* global_scale,
+                                                void* codes, void* scales, uint32_t rows,
+                                                uint32_t k, void* stream) {
+  return mircuda_b200::launch_quantize<false>(input, global_scale, codes, scales, rows, k, stream);
+}
+
+extern "C" int mircuda_b200_nvfp4_quantize_rows_bf16(const void* input, const void* global_scale,
+                                                     void* codes, void* row_scales, uint32_t rows,
+                                                     uint32_t k, void* stream) {
+  return mircuda_b200::launch_quantize<true>(input, global_scale, codes, row_scales, rows, k, stream);
 }

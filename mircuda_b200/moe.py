@@ -125,21 +125,51 @@ class ExpertParallelMoe:
         self.local_experts = experts // self.world
         self.capacity = capacity
         self.nvfp4 = weights.nvfp4
-        if self.nvfp4 and self.world > 1:
-            raise NotImplementedError("NVFP4 expert parallelism needs the grouped quantiser (next)")
+        if self.nvfp4 and self.world > 1 and transport != "peer":
+            raise NotImplementedError("NVFP4 expert parallelism uses the peer transport")
         self.align = 128 if self.nvfp4 else 1
         self.experts = experts
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
-        # One GPU: both transports degenerate to local copies; NVFP4 keeps the block layout
-        # because its groups must start on 128-row scale tiles.
-        self.peer = transport == "peer" and not self.nvfp4
+        # One GPU: both transports degenerate to local copies.
+        self.peer = transport == "peer"
         device = weights.gate_up.device
         rows = capacity if self.peer else self.world * capacity
         groups = self.local_experts if self.peer else self.world * self.local_experts
         self.buffer_rows = rows
         bf16 = dict(dtype=torch.bfloat16, device=device)
         with torch.cuda.stream(stream):
-            if self.peer:
+            # NVFP4 over the peer transport dispatches quantised rows: packed codes (hidden / 2
+            # bytes) and their row-major scales (hidden / 16 bytes), as rows of 2-byte units.
+            self._code_units = hidden // 4
+            self._scale_units = hidden // 32
+            if self.peer and self.nvfp4:
+                if hidden % 256 != 0 or capacity % 128 != 0:
+                    raise plans.InvalidMatmulShape("NVFP4 dispatch needs hidden % 256 == 0 and capacity % 128 == 0")
+                if self.world > 1:
+                    from . import gather
+                    self._codes_symmetric = gather.SymmetricOutput(rows, self._code_units, device, group)
+                    self._scales_symmetric = gather.SymmetricOutput(rows, self._scale_units, device, group)
+                    self._result_symmetric = gather.SymmetricOutput(rows, hidden, device, group)
+                    self.received_codes = self._codes_symmetric.local
+                    self.received_scales = self._scales_symmetric.local
+                    self.expert_out = self._result_symmetric.matrix()
+                    self._code_pointers = self._codes_symmetric.pointers
+                    self._scale_pointers = self._scales_symmetric.pointers
+                    self._result_pointers = self._result_symmetric.pointers
+                else:
+                    self.received_codes = torch.zeros(rows * self._code_units, **bf16)
+                    self.received_scales = torch.zeros(rows * self._scale_units, **bf16)
+                    self.expert_out = torch.zeros(rows, hidden, **bf16)
+                    self._code_pointers = (ctypes.c_void_p * 1)(self.received_codes.data_ptr())
+                    self._scale_pointers = (ctypes.c_void_p * 1)(self.received_scales.data_ptr())
+                    self._result_pointers = (ctypes.c_void_p * 1)(self.expert_out.data_ptr())
+                self.token_codes = torch.zeros(tokens * hidden // 2, dtype=torch.uint8, device=device)
+                self.token_scales = torch.zeros(tokens * hidden // 16, dtype=torch.uint8, device=device)
+                self.all_counts = torch.zeros(self.world * experts, dtype=torch.int32, device=device)
+                self.base_for_me = torch.zeros(experts, dtype=torch.int32, device=device)
+                self.remote_rows = torch.zeros(tokens * top_k, dtype=torch.int32, device=device)
+                self.received_rows = torch.zeros(1, dtype=torch.int32, device=device)
+            elif self.peer:
                 # Buffers peers write into / read from live in symmetric memory, which is only
                 # used to obtain their peer-mapped addresses and a stream-ordered barrier.
                 if self.world > 1:
@@ -173,6 +203,10 @@ class ExpertParallelMoe:
             self.indices = torch.arange(self.local_experts, dtype=torch.int32, device=device).repeat(self.world)
             if self.nvfp4:
                 k1, k2 = hidden, intermediate
+                # Activation scale of the dispatched rows when they are quantised before they
+                # travel: every rank must use the same value (the plans take one alpha per
+                # matrix), so it is fixed at set-up time (`calibrate`) instead of per step.
+                self.dispatch_global = torch.ones(1, dtype=torch.float32, device=device)
                 self.codes1 = torch.zeros(rows * k1 // 2, dtype=torch.uint8, device=device)
                 self.scales1 = torch.zeros(rows // 128 * (k1 // 64) * 512, dtype=torch.uint8, device=device)
                 self.codes2 = torch.zeros(rows * k2 // 2, dtype=torch.uint8, device=device)
@@ -186,6 +220,8 @@ class ExpertParallelMoe:
                 raise plans.InvalidMatmulShape("NVFP4 capacity must be a multiple of 128 rows")
             self.plan1 = _RawGroupedFp4(stream, groups, self.local_experts, capacity, 2 * intermediate, hidden)
             self.plan2 = _RawGroupedFp4(stream, groups, self.local_experts, capacity, hidden, intermediate)
+            if self.peer:
+                self.indices = torch.arange(self.local_experts, dtype=torch.int32, device=device)
         elif self.peer:
             self.plan1 = plans.VariableGroupedBf16Plan(stream, plans.VariableGroupedBf16Spec(
                 groups, capacity, 2 * intermediate, hidden, rows))
@@ -277,7 +313,73 @@ class ExpertParallelMoe:
                 self._p(self.output), self.tokens, self.top_k, self.hidden, handle))
         return self.output
 
+    def calibrate(self, x: torch.Tensor) -> None:
+        """Fixes the activation scale used for rows quantised before dispatch: amax of `x` over
+        all ranks / (448 * 6). Set-up time; call again when the activation range changes."""
+        with torch.cuda.stream(self.stream):
+            amax = x.abs().max().float().reshape(1)
+            if self.world > 1:
+                dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
+            self.dispatch_global.copy_(torch.where(amax > 0, amax / 2688.0, torch.ones_like(amax)))
+
+    def _forward_peer_fp4(self, x, dispatch: Dispatch, routing_weights):
+        lib, handle = self._lib, self._handle()
+        assignments = dispatch.source_rows.numel()
+        pointer_array = ctypes.POINTER(ctypes.c_void_p)
+        rows = self.buffer_rows
+        w = self.weights
+        with torch.cuda.stream(self.stream):
+            # Quantise the rank's token rows once (each is dispatched top_k times), scales
+            # row-major so that codes and scales travel as rows.
+            plans._check(lib.mircuda_b200_nvfp4_quantize_rows_bf16(
+                self._p(x), self._p(self.dispatch_global), self._p(self.token_codes),
+                self._p(self.token_scales), self.tokens, self.hidden, handle))
+            if self.world > 1:
+                dist.all_gather_into_tensor(self.all_counts, dispatch.counts, group=self.group)
+                all_counts = self.all_counts
+            else:
+                all_counts = dispatch.counts
+            plans._check(lib.mircuda_b200_moe_expert_layout(
+                self._p(all_counts), self.world, self.rank, self.experts, 128, self._p(self.base_for_me),
+                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle))
+            for source, pointers, units in ((self.token_codes, self._code_pointers, self._code_units),
+                                            (self.token_scales, self._scale_pointers, self._scale_units)):
+                plans._check(lib.mircuda_b200_moe_dispatch_rows_bf16(
+                    self._p(source), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
+                    self._p(dispatch.position), self._p(self.base_for_me),
+                    ctypes.cast(pointers, pointer_array), self.world, self._p(self.remote_rows),
+                    assignments, self.local_experts, units, handle))
+            if self.world > 1:
+                self._codes_symmetric.barrier()
+            # Row-major scales of the received rows -> 128-row atoms (every expert starts on a
+            # 128-row tile, so the whole buffer is one plain scale matrix).
+            plans._check(lib.mircuda_b200_mxfp8_swizzle_scales(
+                self._p(self.received_scales), self._p(self.scales1), rows, self.hidden // 16, handle))
+            torch.mul(w.gate_up_global, self.dispatch_global, out=self.alphas1[:1])
+            self.alphas1.copy_(self.alphas1[:1].expand_as(self.alphas1))
+            self._timed("gate_up", lambda: self.plan1.execute(
+                self.received_codes, self.scales1, w.gate_up_codes, w.gate_up_scales, self.alphas1,
+                self.indices, self.rows, self.offsets, self.offsets, self.hidden_states))
+            plans._check(lib.mircuda_b200_moe_swiglu_bf16(
+                self._p(self.hidden_states), self._p(self.activated), rows, self._p(self.received_rows),
+                self.intermediate, handle))
+            self._quantize(self.activated, rows, self.intermediate, self.global2, self.codes2, self.scales2)
+            torch.mul(w.down_global, self.global2, out=self.alphas2[:1])
+            self.alphas2.copy_(self.alphas2[:1].expand_as(self.alphas2))
+            self._timed("down", lambda: self.plan2.execute(
+                self.codes2, self.scales2, w.down_codes, w.down_scales, self.alphas2,
+                self.indices, self.rows, self.offsets, self.offsets, self.expert_out))
+            if self.world > 1:
+                self._result_symmetric.barrier()
+            plans._check(lib.mircuda_b200_moe_collect_rows_bf16(
+                ctypes.cast(self._result_pointers, pointer_array), self.world, self._p(dispatch.slots),
+                self._p(dispatch.sorted_experts), self._p(self.remote_rows), self._p(routing_weights),
+                self._p(self.output), self.tokens, self.top_k, self.local_experts, self.hidden, handle))
+        return self.output
+
     def _forward_peer(self, x, dispatch: Dispatch, routing_weights):
+        if self.nvfp4:
+            return self._forward_peer_fp4(x, dispatch, routing_weights)
         lib, handle = self._lib, self._handle()
         assignments = dispatch.source_rows.numel()
         pointer_array = ctypes.POINTER(ctypes.c_void_p)
@@ -288,7 +390,7 @@ class ExpertParallelMoe:
             else:
                 all_counts = dispatch.counts
             plans._check(lib.mircuda_b200_moe_expert_layout(
-                self._p(all_counts), self.world, self.rank, self.experts, self._p(self.base_for_me),
+                self._p(all_counts), self.world, self.rank, self.experts, 1, self._p(self.base_for_me),
                 self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle))
             plans._check(lib.mircuda_b200_moe_dispatch_rows_bf16(
                 self._p(x), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
