@@ -43,6 +43,10 @@ def main() -> None:
                              "GEMMs are then not timed separately)")
     args = parser.parse_args()
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.graph and world > 1:
+        # Capturing the cross-GPU barrier and the count all-gather did not complete when tried
+        # on two GPUs; the graph option is for the single-GPU layer only.
+        raise SystemExit("--graph is only supported on one GPU")
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
