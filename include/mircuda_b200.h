@@ -139,6 +139,26 @@ int mircuda_b200_nvfp4_vector_execute(void* plan, void* stream, const void* inpu
                                       void* output, float global_scale);
 void mircuda_b200_nvfp4_vector_destroy(void* plan);
 
+/* Routed weight-only MXFP8 projection (bf16 activations, MoE decode): assignment a uses input
+ * row a / selections_per_input and matrix selected[a] of weight [matrices, rows, columns]
+ * (E4M3 bytes, row-major E8M0 scales [matrices, rows, columns/32], optional bf16 bias
+ * [matrices, rows], null for none); an out-of-range matrix writes zeros. Replaces
+ * `mircuda_mxfp8_bf16_gathered` (kernels/mxfp8.cu:219-271) and its launch in
+ * src/mxfp8/gathered.rs. columns % 32 == 0, assignments <= 65535. */
+int mircuda_b200_mxfp8_bf16_gathered(const void* input, const void* weight, const void* scales,
+                                     const void* bias, const void* selected, void* output,
+                                     uint32_t assignments, uint32_t matrices, uint32_t rows,
+                                     uint32_t columns, uint32_t selections_per_input,
+                                     void* stream);
+/* MXFP8 embedding lookup: output[t, :] = bf16(e4m3(W[row]) * 2^(s - 127) * output_scale) for
+ * row = selected[selected_start + t]; rows >= vocab leave their output row untouched. Bit-
+ * identical to `mircuda_mxfp8_embedding_bf16` (kernels/mxfp8.cu:273-296), which it replaces.
+ * hidden % 32 == 0, tokens <= 65535. */
+int mircuda_b200_mxfp8_embedding_bf16(const void* weight, const void* scales,
+                                      const void* selected, void* output,
+                                      uint32_t selected_start, uint32_t tokens, uint32_t vocab,
+                                      uint32_t hidden, float output_scale, void* stream);
+
 /* bf16 [rows, k] -> NVFP4 codes [rows, k/2] + swizzled UE4M3 scales per 16, given the
  * tensor's global scale (amax / 2688) in device memory. NEW: the reference has no NVFP4
  * quantizer. `mircuda_b200_nvfp4_global_scale` computes that scale into *global_scale
