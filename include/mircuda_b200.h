@@ -316,6 +316,18 @@ int mircuda_marlin_mxfp4_moe_execute(void* stream, const void* input, const void
                                      int input_features, int thread_config, void* locks,
                                      bool atomic_reduce);
 
+/* ------------------------------------------------------- blockwise-scaled FP8 GEMV ----
+ * y[n] = bf16(sum_b input_scales[b] * weight_scales[n/128 + b * (n/128)] * sum_{k in block b}
+ * e4m3(x[k]) * e4m3(W[n, k])), 128-element K blocks, fp32 scales; n % 128 == 0, k % 128 == 0.
+ * Replaces sys/native/fp8_vector_sm120.cu:92-142, declared in
+ * sys/src/platform/cutlass/fp8_vector.rs. workspace_bytes is always 0. */
+int mircuda_fp8_vector_create(int n, int k, void* stream, void** output);
+size_t mircuda_fp8_vector_workspace_bytes(const void* plan);
+int mircuda_fp8_vector_execute(void* plan, void* stream, const void* input,
+                               const void* input_scales, const void* weight,
+                               const void* weight_scales, void* output);
+void mircuda_fp8_vector_destroy(void* plan);
+
 /* ------------------------------------------------------------- dense f16 / bf16 GEMM ----
  * C[m, n] = alpha * A[m, k] . B[n, k]^T + beta * C; input_type 0 = f16, 1 = bf16; output_type
  * = input_type or 2 (f32). Any shape: k and n multiples of 8 run on tcgen05, others on a

@@ -72,6 +72,10 @@ SIGNATURES.update({
     "mircuda_marlin_mxfp4_moe_execute": (_i, [_vp] * 10 + [_i, _b, _i, _i, _i, _i, _vp, _b]),
     "mircuda_b200_mxfp8_bf16_gathered": (_i, [_vp] * 6 + [_u32] * 5 + [_vp]),
     "mircuda_b200_mxfp8_embedding_bf16": (_i, [_vp] * 4 + [_u32] * 4 + [_f, _vp]),
+    "mircuda_fp8_vector_create": (_i, [_i, _i, _vp, _vpp]),
+    "mircuda_fp8_vector_workspace_bytes": (_sz, [_vp]),
+    "mircuda_fp8_vector_execute": (_i, [_vp] * 7),
+    "mircuda_fp8_vector_destroy": (None, [_vp]),
     "mircuda_dense_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_dense_workspace_bytes": (_sz, [_vp]),
     "mircuda_dense_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _f]),

@@ -127,3 +127,55 @@ class W4A16Plan:
             self._raw = None
 
     __del__ = close
+
+
+@dataclass(frozen=True)
+class BlockwiseFp8VectorSpec:
+    """``BlockwiseFp8VectorSpec`` (src/cutlass/fp8_vector.rs): E4M3 vector x E4M3 [n, k] matrix
+    with one fp32 scale per 128 input elements and per 128 x 128 weight block."""
+    n: int
+    k: int
+
+    def __post_init__(self):
+        if self.n <= 0 or self.k <= 0 or self.n % 128 != 0 or self.k % 128 != 0:
+            raise InvalidMatmulShape("n and k must be positive multiples of 128")
+
+    def input_scale_elements(self) -> int:
+        return self.k // 128
+
+    def weight_scale_elements(self) -> int:
+        return (self.n // 128) * (self.k // 128)
+
+
+class BlockwiseFp8VectorPlan:
+    """``BlockwiseFp8VectorPlan`` over ``mircuda_fp8_vector_*``."""
+
+    def __init__(self, stream, spec: BlockwiseFp8VectorSpec):
+        self._lib = _lib.load()
+        self.spec, self._stream = spec, stream
+        raw = ctypes.c_void_p()
+        _check(self._lib.mircuda_fp8_vector_create(spec.n, spec.k, _stream_handle(stream),
+                                                   ctypes.byref(raw)))
+        self._raw = raw
+
+    def execute(self, stream, input, input_scales, weight, weight_scales, output) -> None:
+        if stream.cuda_stream != self._stream.cuda_stream:
+            raise StreamMismatch()
+        s = self.spec
+        _exact("input", s.k, input)
+        _exact("input scales", s.input_scale_elements(), input_scales)
+        _exact("weight", s.n * s.k, weight)
+        _exact("weight scales", s.weight_scale_elements(), weight_scales)
+        _exact("output", s.n, output)
+        bytes_ = (torch.uint8, torch.int8)
+        _check(self._lib.mircuda_fp8_vector_execute(
+            self._raw, _stream_handle(stream), _device_pointer(input, bytes_),
+            _device_pointer(input_scales, (torch.float32,)), _device_pointer(weight, bytes_),
+            _device_pointer(weight_scales, (torch.float32,)), _device_pointer(output, (torch.bfloat16,))))
+
+    def close(self) -> None:
+        if getattr(self, "_raw", None):
+            self._lib.mircuda_fp8_vector_destroy(self._raw)
+            self._raw = None
+
+    __del__ = close

@@ -119,3 +119,43 @@ def test_w4a16_nibble_order(cuda_stream):
     cuda_stream.synchronize()
     plan.close()
     assert (out.float() == float(sum(range(0, k, 2)))).all()
+
+
+def test_fp8_vector_golden(cuda_stream):
+    """blockwise_fp8_vector_produces_bf16 (tests/cutlass/fp8.rs:12-34): ones, unit scales -> 128."""
+    from mircuda_b200 import dense
+    n = k = 128
+    x = torch.full((k,), 0x38, dtype=torch.uint8, device="cuda")
+    w = torch.full((n * k,), 0x38, dtype=torch.uint8, device="cuda")
+    ones = torch.ones(1, dtype=torch.float32, device="cuda")
+    out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    plan = dense.BlockwiseFp8VectorPlan(cuda_stream, dense.BlockwiseFp8VectorSpec(n, k))
+    torch.cuda.synchronize()
+    plan.execute(cuda_stream, x, ones, w, ones.clone(), out)
+    cuda_stream.synchronize()
+    plan.close()
+    assert (out.float() == 128.0).all()
+
+
+def test_fp8_vector_random(cuda_stream):
+    import oracle
+    from mircuda_b200 import dense
+    n, k = 1152, 2048
+    rng = np.random.default_rng(515)
+    x = rng.integers(0, 256, size=k, dtype=np.uint8)
+    w = rng.integers(0, 256, size=(n, k), dtype=np.uint8)
+    x[(x & 0x7F) == 0x7F] = 0x38
+    w[(w & 0x7F) == 0x7F] = 0x38
+    sa = rng.uniform(0.5, 2.0, size=k // 128).astype(np.float32)
+    sb = rng.uniform(0.01, 0.05, size=(k // 128, n // 128)).astype(np.float32)   # [block, n / 128]
+    table = oracle.e4m3_table().astype(np.float64)
+    products = (table[w].reshape(n, k // 128, 128) * table[x].reshape(1, k // 128, 128)).sum(axis=2)
+    expected = (products * sa[None, :] * sb.T.repeat(128, axis=0)).sum(axis=1)
+    out = torch.zeros(n, dtype=torch.bfloat16, device="cuda")
+    plan = dense.BlockwiseFp8VectorPlan(cuda_stream, dense.BlockwiseFp8VectorSpec(n, k))
+    torch.cuda.synchronize()
+    plan.execute(cuda_stream, torch.from_numpy(x).cuda(), torch.from_numpy(sa).cuda(),
+                 torch.from_numpy(w.reshape(-1)).cuda(), torch.from_numpy(sb.reshape(-1)).cuda(), out)
+    cuda_stream.synchronize()
+    plan.close()
+    assert_close(out, torch.from_numpy(expected), "blockwise fp8 vector")
