@@ -75,10 +75,11 @@ def embedding(stream, words, scales, selected, start, tokens, vocab, hidden, out
     library = _lib.load()
     d_words = torch.from_numpy(words.view(np.int32)).cuda()
     d_selected = torch.from_numpy(np.asarray(selected, np.uint32).view(np.int32)).cuda()
+    d_scales = u8(scales)
     out = torch.full((tokens * hidden,), fill, dtype=torch.bfloat16, device="cuda")
     torch.cuda.synchronize()
     assert library.mircuda_b200_mxfp8_embedding_bf16(
-        pointer(d_words), pointer(u8(scales)), pointer(d_selected), pointer(out), start, tokens, vocab,
+        pointer(d_words), pointer(d_scales), pointer(d_selected), pointer(out), start, tokens, vocab,
         hidden, ctypes.c_float(output_scale), ctypes.c_void_p(stream.cuda_stream)) == 0
     stream.synchronize()
     return bf16_bits(out).reshape(tokens, hidden)
