@@ -1,0 +1,88 @@
+"""Host-side mirrors added after the first milestone: spec validation, buffer-size rules and
+the int4 weight quantiser, all on CPU; argument validation of the newer C entry points."""
+import ctypes
+
+import pytest
+import torch
+
+
+@pytest.fixture(scope="module")
+def library():
+    from mircuda_b200 import build, _lib
+    build.build_library()
+    return _lib.load()
+
+
+def test_variable_grouped_fp4_spec_sizes():
+    """sys/src/platform/cutlass/variable_grouped/fp4/mod.rs:150-223: scale capacity and bytes."""
+    from mircuda_b200 import plans, plans_fp4
+    spec = plans_fp4.VariableGroupedFp4Spec(4, 3, 4, 128, 128, 6)
+    assert spec.scale_capacity_rows() == (6 + 127 * 4) // 128 * 128 == 512
+    assert spec.a_scale_bytes() == 4 * (128 // 64) * 512          # tests/cutlass/grouped/fp4.rs:47-48
+    assert spec.b_scale_bytes() == 3 * (128 // 64) * 512
+    with pytest.raises(plans.InvalidMatmulShape):
+        plans_fp4.VariableGroupedFp4Spec(4, 3, 4, 128, 96, 6)      # k % 64
+    with pytest.raises(plans.InvalidMatmulShape):
+        plans_fp4.VariableGroupedFp4Spec(0, 3, 4, 128, 128, 6)
+
+
+def test_indexed_grouped_fp4_spec():
+    from mircuda_b200 import plans, plans_fp4
+    spec = plans_fp4.IndexedGroupedFp4Spec(64, 33, 1, 128, 128)
+    assert spec.inputs() == 64 and spec.with_broadcast_input().inputs() == 1
+    with pytest.raises(plans.InvalidMatmulShape):
+        plans_fp4.IndexedGroupedFp4Spec(64, 33, 1, 128, 100)
+
+
+def test_dense_and_w4a16_specs():
+    from mircuda_b200 import dense, plans
+    assert dense.DenseMatmulSpec(2, 4, 3).output() == torch.bfloat16
+    assert dense.DenseMatmulSpec(1, 128, 128, torch.bfloat16, torch.float32).output() == torch.float32
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.DenseMatmulSpec(1, 128, 128, torch.float32)
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.DenseMatmulSpec(1, 128, 128, torch.float16, torch.bfloat16)
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.W4A16Spec(1, 128, 100)
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.BlockwiseFp8VectorSpec(100, 128)
+    assert dense.BlockwiseFp8VectorSpec(256, 512).weight_scale_elements() == 8
+
+
+def test_quantize_int4_round_trip():
+    """max|w| / 7 per 128 elements, zero point 8, even k in the low nibble."""
+    from mircuda_b200 import dense
+    generator = torch.Generator().manual_seed(3)
+    weight = torch.randn(16, 256, generator=generator) * 0.02
+    packed, scales = dense.quantize_int4(weight)
+    assert packed.shape == (16, 128) and scales.shape == (16, 2) and scales.dtype == torch.float16
+    codes = torch.stack([packed & 15, packed >> 4], dim=-1).reshape(16, 256).float()
+    restored = (codes - 8.0) * scales.float().repeat_interleave(128, dim=1)
+    step = scales.float().repeat_interleave(128, dim=1)
+    assert ((restored - weight).abs() <= 0.5 * step + 1e-6).all()
+    assert codes.max() <= 15 and codes.min() >= 1          # symmetric: -7..7 around 8
+    zero_packed, zero_scales = dense.quantize_int4(torch.zeros(8, 128))
+    assert (zero_packed == 0x88).all() and (zero_scales == 0).all()
+
+
+def test_new_entry_points_validate_without_a_gpu(library):
+    raw = ctypes.c_void_p()
+    fake = ctypes.c_void_p(0x10)
+    assert library.mircuda_variable_grouped_fp4_create(4, 3, 4, 128, 100, fake, ctypes.byref(raw)) == -1
+    assert library.mircuda_grouped_fp4_create(4, 3, 4, 128, 128, False, None, ctypes.byref(raw)) == -1
+    assert library.mircuda_dense_create(2, 2, 4, 4, 4, fake, ctypes.byref(raw)) == -1     # f32 inputs
+    assert library.mircuda_dense_create(0, 1, 4, 4, 4, fake, ctypes.byref(raw)) == -1     # f16 -> bf16
+    assert library.mircuda_b200_w4a16_create(1, 128, 100, fake, ctypes.byref(raw)) == -1
+    assert library.mircuda_fp8_vector_create(100, 128, fake, ctypes.byref(raw)) == -1
+    assert library.mircuda_b200_moe_swiglu_bf16(None, None, 1, None, 8, fake) == -1
+    assert library.mircuda_b200_moe_expert_layout(None, 2, 0, 8, 1, None, None, None, None, fake) == -1
+    assert library.mircuda_b200_mxfp8_bf16_gathered(None, None, None, None, None, None, 1, 1, 1, 32, 1, fake) == -1
+    assert library.mircuda_marlin_nvfp4_moe_execute(fake, None, None, None, None, None, None, None, None,
+                                                    None, None, 1, False, 1, 64, 64, 0, None, False) == -1
+    assert library.mircuda_dense_workspace_bytes(None) == 0
+    assert library.mircuda_fp8_vector_workspace_bytes(None) == 0
+    library.mircuda_variable_grouped_fp4_destroy(None)
+    library.mircuda_grouped_fp4_destroy(None)
+    library.mircuda_dense_destroy(None)
+    library.mircuda_b200_w4a16_destroy(None)
+    library.mircuda_fp8_vector_destroy(None)
