@@ -45,7 +45,11 @@ struct Layout {
   static constexpr uint32_t kBarrierOffset = kBOffset + STAGES * kBBytes;
   static constexpr uint32_t kBarriers = 2 * STAGES + 2 * ACC_STAGES;
   static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
-  static constexpr uint32_t kDynamicBytes = kMiscOffset + 16 + 1024;
+  // Tile starts of up to kSharedGroups groups, copied once per CTA: the per-tile binary search
+  // then runs on shared memory instead of on a chain of dependent L2 round trips.
+  static constexpr uint32_t kSharedGroups = 2048;
+  static constexpr uint32_t kStartsOffset = kMiscOffset + 16;
+  static constexpr uint32_t kDynamicBytes = kStartsOffset + (kSharedGroups + 1) * 4 + 1024;
   static_assert(ACC_STAGES * BN <= kTmemColumns, "tensor memory budget");
   static_assert(kDynamicBytes <= 232448, "shared memory budget");
 };
@@ -111,20 +115,21 @@ struct Tile {
 };
 
 // Linear tile index -> tile. Inside a group, row tiles vary fastest.
-__device__ __forceinline__ Tile locate(uint32_t index, const uint32_t* __restrict__ tile_starts,
+// `starts` is the shared-memory copy of tile_starts when the groups fit, else the global array.
+__device__ __forceinline__ Tile locate(uint32_t index, const uint32_t* starts,
                                        const unsigned int* __restrict__ rows,
                                        const unsigned int* __restrict__ offsets, uint32_t groups,
                                        uint32_t max_rows, uint32_t block_n) {
   uint32_t low = 0u, high = groups;       // last group whose start is <= index
   while (high - low > 1u) {
     const uint32_t middle = (low + high) / 2u;
-    if (__ldg(tile_starts + middle) <= index) low = middle; else high = middle;
+    if (starts[middle] <= index) low = middle; else high = middle;
   }
   // Groups without tiles share their start with the next group; step past them.
-  while (low + 1u < groups && __ldg(tile_starts + low + 1u) <= index) ++low;
+  while (low + 1u < groups && starts[low + 1u] <= index) ++low;
   const uint32_t row_count = min(__ldg(rows + low), max_rows);
   const uint32_t row_tiles = (row_count + kBlockM - 1u) / kBlockM;
-  const uint32_t local = index - __ldg(tile_starts + low);
+  const uint32_t local = index - starts[low];
   const uint32_t row_tile = local % row_tiles;
   Tile tile;
   tile.group = low;
@@ -177,6 +182,14 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
     ptx::tmem_allocate(tmem_slot, kTmemColumns);
     ptx::tmem_relinquish();
   }
+  uint32_t* starts_table = reinterpret_cast<uint32_t*>(shared + L::kStartsOffset);
+  const uint32_t* starts = tile_starts;
+  if (groups <= L::kSharedGroups) {
+    for (uint32_t group = threadIdx.x; group <= groups; group += kThreads) {
+      starts_table[group] = __ldg(tile_starts + group);
+    }
+    starts = starts_table;
+  }
   ptx::tcgen05_fence_before();
   __syncthreads();
   ptx::tcgen05_fence_after();
@@ -189,9 +202,20 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
     if (ptx::elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool running = true;
+      // The next tile's routing is fetched while this tile's loads are being issued.
+      Tile upcoming = {};
+      uint32_t upcoming_matrix = 0u;
+      if (blockIdx.x < tiles) {
+        upcoming = locate(blockIdx.x, starts, rows, offsets, groups, max_rows, BN);
+        upcoming_matrix = indices == nullptr ? upcoming.group : __ldg(indices + upcoming.group);
+      }
       for (uint32_t index = blockIdx.x; running && index < tiles; index += gridDim.x) {
-        const Tile tile = locate(index, tile_starts, rows, offsets, groups, max_rows, BN);
-        const uint32_t matrix = indices == nullptr ? tile.group : __ldg(indices + tile.group);
+        const Tile tile = upcoming;
+        const uint32_t matrix = upcoming_matrix;
+        if (index + gridDim.x < tiles) {
+          upcoming = locate(index + gridDim.x, starts, rows, offsets, groups, max_rows, BN);
+          upcoming_matrix = indices == nullptr ? upcoming.group : __ldg(indices + upcoming.group);
+        }
         for (uint32_t kt = 0; kt < k_tiles; ++kt) {
           if (!ptx::mbarrier_wait(&empty[stage], phase ^ 1u, abort)) {
             running = false;
@@ -273,7 +297,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
     const uint32_t quarter = warp % 4u;
     uint32_t acc_stage = 0, acc_phase = 0;
     for (uint32_t index = blockIdx.x; index < tiles; index += gridDim.x) {
-      const Tile tile = locate(index, tile_starts, rows, offsets, groups, max_rows, BN);
+      const Tile tile = locate(index, starts, rows, offsets, groups, max_rows, BN);
       if (!ptx::mbarrier_wait(&acc_full[acc_stage], acc_phase, abort)) break;
       ptx::tcgen05_fence_after();
       const uint32_t row_in_tile = quarter * 32u + lane;

@@ -57,6 +57,7 @@ constexpr int kMaxParts = 8;
 struct Plan {
   int m, n, k;
   int parts;                 // K parts = cluster size along y
+  bool overlap_launches;     // programmatic dependent launch (MIRCUDA_B200_OVERLAP_LAUNCHES=1)
   int device;
   cudaStream_t stream;
   uint32_t* status;          // pinned; set when a bounded wait ran out
@@ -167,6 +168,12 @@ nvfp4_vector_kernel(const __grid_constant__ CUtensorMap weight_map,
     ptx::prefetch_tensor_map(&weight_map);
   }
   __syncthreads();
+  // Programmatic dependent launch (a no-op unless the launch asked for it): the next kernel
+  // in the stream may start as soon as every CTA of this one has got here, and this kernel
+  // may have started before the previous one finished. Weights and their scales are taken to
+  // be constant, so the producer streams them at once; every thread waits for the previous
+  // kernel to complete before it first reads activations or writes outputs.
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   if (warp == kConsumerWarps) {
     // --------------------------------------------------------------------- producer
@@ -192,8 +199,10 @@ nvfp4_vector_kernel(const __grid_constant__ CUtensorMap weight_map,
         for (int spin = 0; spin < 256; ++spin) __nanosleep(1000);
       }
     }
+    asm volatile("griddepcontrol.wait;" ::: "memory");
   } else {
     // -------------------------------------------------------------------- consumers
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int group = lane >> 2;                     // weight row inside a 16-row step / token
     const int quad = lane & 3;
     const int warp_k = warp % kWarpsK;               // 128-element K sub-range of the stage
@@ -382,6 +391,10 @@ extern "C" int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* strea
   }
   *plan->status = 0u;
   plan->parts = parts_for(n, k, sm_count);
+  // Opt-in: with it, this kernel may read its weights while the previous kernel of the stream
+  // is still running, so the caller must not let that kernel write them.
+  const char* overlap = std::getenv("MIRCUDA_B200_OVERLAP_LAUNCHES");
+  plan->overlap_launches = overlap != nullptr && overlap[0] == '1';
   if (const char* forced = std::getenv("MIRCUDA_B200_NVFP4_PARTS")) {
     const int value = std::atoi(forced);
     const int stages = (k + kStageK - 1) / kStageK;
@@ -427,13 +440,15 @@ extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const 
   config.blockDim = dim3(kThreads, 1, 1);
   config.dynamicSmemBytes = SharedLayout::kBytes;
   config.stream = cuda_stream;
-  cudaLaunchAttribute attribute = {};
-  attribute.id = cudaLaunchAttributeClusterDimension;
-  attribute.val.clusterDim.x = 1;
-  attribute.val.clusterDim.y = plan->parts;
-  attribute.val.clusterDim.z = 1;
-  config.attrs = &attribute;
-  config.numAttrs = 1;
+  cudaLaunchAttribute attributes[2] = {};
+  attributes[0].id = cudaLaunchAttributeClusterDimension;
+  attributes[0].val.clusterDim.x = 1;
+  attributes[0].val.clusterDim.y = plan->parts;
+  attributes[0].val.clusterDim.z = 1;
+  attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attributes[1].val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = attributes;
+  config.numAttrs = plan->overlap_launches ? 2 : 1;
   return static_cast<int>(cudaLaunchKernelEx(
       &config, nvfp4_vector_kernel, plan->weight_map, static_cast<const __nv_bfloat16*>(input),
       static_cast<const uint8_t*>(weight_scales), static_cast<__nv_bfloat16*>(output), plan->m,
