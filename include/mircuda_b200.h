@@ -286,6 +286,18 @@ int mircuda_b200_moe_dispatch_rows_bf16(const void* source, const int* source_in
                                         const int* base_for_me, void* const* receive_buffers,
                                         uint32_t world, int* remote_row, uint32_t count,
                                         uint32_t local_experts, uint32_t columns, void* stream);
+/* Row-major scale bytes [rows, columns] (as dispatched) -> the 128-row x 4-column atoms the
+ * block-scaled plans read, for the first min(rows, *row_bound) rows (row_bound may be null);
+ * columns % 16 == 0. Same permutation as mircuda_b200_mxfp8_swizzle_scales, 16 bytes a thread. */
+int mircuda_b200_moe_scale_atoms(const void* row_scales, void* atoms, uint32_t rows,
+                                 const unsigned int* row_bound, uint32_t columns, void* stream);
+/* SwiGLU fused with the NVFP4 quantiser: input [rows, 2*intermediate] bf16 (gate then up),
+ * outputs the codes [rows, intermediate/2] and swizzled scales of bf16(silu(gate) * up) for a
+ * given (device) global scale, without writing the activated tensor; identical, bit for bit,
+ * to mircuda_b200_moe_swiglu_bf16 followed by mircuda_b200_nvfp4_quantize_bf16. */
+int mircuda_b200_moe_swiglu_nvfp4(const void* input, const void* global_scale, void* codes,
+                                  void* scales, uint32_t rows, const unsigned int* row_bound,
+                                  uint32_t intermediate, void* stream);
 int mircuda_b200_moe_collect_rows_bf16(void* const* result_buffers, uint32_t world, const int* slot,
                                        const int* sorted_expert, const int* remote_row,
                                        const float* weights, void* output, uint32_t tokens,

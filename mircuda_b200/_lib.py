@@ -84,6 +84,8 @@ SIGNATURES.update({
     "mircuda_b200_w4a16_workspace_bytes": (_sz, [_vp]),
     "mircuda_b200_w4a16_execute": (_i, [_vp] * 6),
     "mircuda_b200_w4a16_destroy": (None, [_vp]),
+    "mircuda_b200_moe_scale_atoms": (_i, [_vp, _vp, _u32, _vp, _u32, _vp]),
+    "mircuda_b200_moe_swiglu_nvfp4": (_i, [_vp, _vp, _vp, _vp, _u32, _vp, _u32, _vp]),
     "mircuda_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_variable_grouped_fp4_execute": (_i, [_vp] * 12),
     "mircuda_variable_grouped_fp4_destroy": (None, [_vp]),

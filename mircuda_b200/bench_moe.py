@@ -103,7 +103,7 @@ def main() -> None:
         layer = moe.ExpertParallelMoe(stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, local_tokens,
                                       capacity, bank, transport=args.transport)
         if nvfp4:
-            layer.calibrate(x)
+            layer.calibrate(x, dispatch, weights)
 
         def barrier():
             stream.synchronize()
@@ -157,9 +157,10 @@ def main() -> None:
             "scaling": "strong", "data": "synthetic",
             "gemm": {name: {"ms": gemm_ms[name],
                             "tflops_per_gpu": flops[name] / world / (gemm_ms[name] * 1e-3) / 1e12}
-                     for name in gemm_ms},
-            "gemm_tflops_all_gpus": (sum(flops.values()) / (sum(gemm_ms.values()) * 1e-3) / 1e12
+                     for name in gemm_ms if name in flops},
+            "gemm_tflops_all_gpus": (sum(flops.values()) / (sum(gemm_ms[name] for name in flops) * 1e-3) / 1e12
                                      if gemm_ms else None),
+            "stage_ms_rank0": {name: round(value, 4) for name, value in gemm_ms.items() if name not in flops},
             "cuda_graph": bool(args.graph),
             "config": {"workload": "qwen3-30b-a3b moe feed-forward", "experts": EXPERTS, "top_k": TOP_K,
                        "hidden": HIDDEN, "intermediate": INTERMEDIATE, "tokens": TOKENS,

@@ -191,6 +191,9 @@ moe_dispatch_rows_kernel(const uint4* __restrict__ source, const int* __restrict
 // Combine over peer memory: every token reads its top_k expert rows from the owners' output
 // buffers (peer loads) and adds them with its routing weights. slot[t, j] is the position of
 // (token, choice) in the expert-sorted assignment list.
+// All top_k rows of a piece are requested before the first is used: their row indices and
+// weights are read once per token (lane j holds choice j) and broadcast.
+template <int TOP_K>
 __global__ void __launch_bounds__(kThreads)
 moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
                         const int* __restrict__ sorted_expert, const int* __restrict__ remote_row,
@@ -199,26 +202,62 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t token = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; token < tokens; token += warps) {
+    const uint4* my_row = nullptr;
+    float my_weight = 0.0f;
+    if (lane < top_k) {
+      const int item = __ldg(slot + token * top_k + lane);
+      const uint32_t owner = static_cast<uint32_t>(__ldg(sorted_expert + item)) / local_experts;
+      my_row = static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(remote_row[item]) * pieces;
+      my_weight = __ldg(weights + token * top_k + lane);
+    }
     for (uint32_t piece = lane; piece < pieces; piece += 32u) {
+      uint4 values[TOP_K];
+      float scale[TOP_K];
+#pragma unroll
+      for (int choice = 0; choice < TOP_K; ++choice) {
+        const uint4* row = reinterpret_cast<const uint4*>(
+            __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), choice));
+        scale[choice] = __shfl_sync(0xffffffffu, my_weight, choice);
+        values[choice] = static_cast<uint32_t>(choice) < top_k ? row[piece] : make_uint4(0u, 0u, 0u, 0u);
+      }
       float sums[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (uint32_t choice = 0; choice < top_k; ++choice) {
-        const int item = __ldg(slot + token * top_k + choice);
-        const uint32_t owner = static_cast<uint32_t>(__ldg(sorted_expert + item)) / local_experts;
-        const int row = remote_row[item];
-        const float weight = __ldg(weights + token * top_k + choice);
-        const uint4 value =
-            *(static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(row) * pieces + piece);
-        const uint32_t words[4] = {value.x, value.y, value.z, value.w};
+#pragma unroll
+      for (int choice = 0; choice < TOP_K; ++choice) {
+        const uint32_t words[4] = {values[choice].x, values[choice].y, values[choice].z, values[choice].w};
 #pragma unroll
         for (int word = 0; word < 4; ++word) {
           const float2 pair = unpack(words[word]);
-          sums[2 * word] = fmaf(weight, pair.x, sums[2 * word]);
-          sums[2 * word + 1] = fmaf(weight, pair.y, sums[2 * word + 1]);
+          sums[2 * word] = fmaf(scale[choice], pair.x, sums[2 * word]);
+          sums[2 * word + 1] = fmaf(scale[choice], pair.y, sums[2 * word + 1]);
         }
       }
       output[static_cast<size_t>(token) * pieces + piece] =
           make_uint4(pack(sums[0], sums[1]), pack(sums[2], sums[3]), pack(sums[4], sums[5]),
                      pack(sums[6], sums[7]));
+    }
+  }
+}
+
+// Row-major scale bytes [rows, columns] -> 512-byte atoms of 128 rows x 4 columns, 16 columns
+// (four 4-byte atom pieces) per thread, only the first min(rows, *row_bound) rows.
+__global__ void __launch_bounds__(kThreads)
+moe_scale_atoms_kernel(const uint4* __restrict__ input, uint8_t* __restrict__ output, uint32_t rows,
+                       const unsigned int* __restrict__ row_bound, uint32_t columns) {
+  if (row_bound != nullptr) rows = min(rows, __ldg(row_bound));
+  const uint32_t vectors = columns / 16u;
+  const size_t total = static_cast<size_t>(rows) * vectors;
+  const uint32_t column_tiles = columns / 4u;
+  for (size_t item = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; item < total;
+       item += static_cast<size_t>(gridDim.x) * kThreads) {
+    const uint32_t row = static_cast<uint32_t>(item / vectors);
+    const uint32_t vector = static_cast<uint32_t>(item - static_cast<size_t>(row) * vectors);
+    const uint4 value = __ldg(input + item);
+    const uint32_t words[4] = {value.x, value.y, value.z, value.w};
+    uint8_t* base = output + (static_cast<size_t>(row / 128u) * column_tiles + vector * 4u) * 512u +
+                    (row % 32u) * 16u + ((row % 128u) / 32u) * 4u;
+#pragma unroll
+    for (int tile = 0; tile < 4; ++tile) {
+      *reinterpret_cast<uint32_t*>(base + tile * 512) = words[tile];
     }
   }
 }
@@ -347,7 +386,7 @@ extern "C" int mircuda_b200_moe_collect_rows_bf16(
   using namespace mircuda_b200::moe_rows;
   if (result_buffers == nullptr || slot == nullptr || sorted_expert == nullptr ||
       remote_row == nullptr || weights == nullptr || output == nullptr || world == 0 || world > 8 ||
-      top_k == 0 || local_experts == 0 || columns == 0 || columns % 8 != 0 || !aligned16(output)) {
+      top_k == 0 || top_k > 32 || local_experts == 0 || columns == 0 || columns % 8 != 0 || !aligned16(output)) {
     return -1;
   }
   PeerBases results = {};
@@ -356,9 +395,30 @@ extern "C" int mircuda_b200_moe_collect_rows_bf16(
     results.base[peer] = result_buffers[peer];
   }
   if (tokens == 0) return 0;
-  moe_collect_rows_kernel<<<grid_for(tokens, kThreads / 32), kThreads, 0,
-                            static_cast<cudaStream_t>(stream)>>>(
-      results, slot, sorted_expert, remote_row, weights, static_cast<uint4*>(output), tokens, top_k,
-      local_experts, columns / 8u);
+  const int grid = grid_for(tokens, kThreads / 32);
+  auto cuda_stream = static_cast<cudaStream_t>(stream);
+  if (top_k <= 8) {
+    moe_collect_rows_kernel<8><<<grid, kThreads, 0, cuda_stream>>>(
+        results, slot, sorted_expert, remote_row, weights, static_cast<uint4*>(output), tokens, top_k,
+        local_experts, columns / 8u);
+  } else {
+    moe_collect_rows_kernel<32><<<grid, kThreads, 0, cuda_stream>>>(
+        results, slot, sorted_expert, remote_row, weights, static_cast<uint4*>(output), tokens, top_k,
+        local_experts, columns / 8u);
+  }
+  return static_cast<int>(cudaPeekAtLastError());
+}
+
+extern "C" int mircuda_b200_moe_scale_atoms(const void* row_scales, void* atoms, uint32_t rows,
+                                            const unsigned int* row_bound, uint32_t columns,
+                                            void* stream) {
+  using namespace mircuda_b200::moe_rows;
+  if (row_scales == nullptr || atoms == nullptr || rows == 0 || columns == 0 || columns % 16 != 0 ||
+      !aligned16(row_scales) || (reinterpret_cast<uintptr_t>(atoms) & 3u) != 0u) {
+    return -1;
+  }
+  const size_t total = static_cast<size_t>(rows) * (columns / 16u);
+  moe_scale_atoms_kernel<<<grid_for(total, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(row_scales), static_cast<uint8_t*>(atoms), rows, row_bound, columns);
   return static_cast<int>(cudaPeekAtLastError());
 }

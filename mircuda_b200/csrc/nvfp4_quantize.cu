@@ -70,16 +70,47 @@ __device__ __forceinline__ uint32_t encode_e2m1_pair(float low, float high) {
 // One thread per 16-element block: two 16-byte loads, one 8-byte store, one scale byte.
 // ROW_MAJOR_SCALES: scales go to [rows, k/16] bytes instead of the swizzled atoms, so that
 // whole rows (codes and scales) can be moved to another place before the layout is fixed.
-template <bool ROW_MAJOR_SCALES>
+// SwiGLU of eight (gate, up) bf16 pairs -> eight bf16, as the stand-alone SwiGLU kernel
+// computes and rounds them.
+__device__ __forceinline__ uint4 swiglu8(const uint4& gate, const uint4& up) {
+  const uint32_t gates[4] = {gate.x, gate.y, gate.z, gate.w};
+  const uint32_t ups[4] = {up.x, up.y, up.z, up.w};
+  uint32_t packed[4];
+#pragma unroll
+  for (int word = 0; word < 4; ++word) {
+    const float g_low = __uint_as_float(gates[word] << 16);
+    const float g_high = __uint_as_float(gates[word] & 0xffff0000u);
+    const float u_low = __uint_as_float(ups[word] << 16);
+    const float u_high = __uint_as_float(ups[word] & 0xffff0000u);
+    const __nv_bfloat162 two = __floats2bfloat162_rn(g_low / (1.0f + __expf(-g_low)) * u_low,
+                                                     g_high / (1.0f + __expf(-g_high)) * u_high);
+    packed[word] = *reinterpret_cast<const uint32_t*>(&two);
+  }
+  return make_uint4(packed[0], packed[1], packed[2], packed[3]);
+}
+
+// SWIGLU: the input is [rows, 2k] (gate columns then up columns) and the quantised tensor is
+// silu(gate) * up rounded to bf16, which is never written to memory.
+template <bool ROW_MAJOR_SCALES, bool SWIGLU>
 __global__ void __launch_bounds__(256)
 nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
                 uint2* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t rows,
-                uint32_t k) {
+                const unsigned int* __restrict__ row_bound, uint32_t k) {
+  if (row_bound != nullptr) rows = min(rows, __ldg(row_bound));
   const uint32_t blocks_per_row = k / 16u;
   const size_t block = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (block >= static_cast<size_t>(rows) * blocks_per_row) return;
-  const uint4 first = __ldg(input + block * 2u);
-  const uint4 second = __ldg(input + block * 2u + 1u);
+  uint4 first, second;
+  if (SWIGLU) {
+    const size_t row_index = block / blocks_per_row;
+    const size_t vector = row_index * (blocks_per_row * 4u) + (block - row_index * blocks_per_row) * 2u;
+    const size_t up = vector + blocks_per_row * 2u;       // k / 8 sixteen-byte vectors further
+    first = swiglu8(__ldg(input + vector), __ldg(input + up));
+    second = swiglu8(__ldg(input + vector + 1u), __ldg(input + up + 1u));
+  } else {
+    first = __ldg(input + block * 2u);
+    second = __ldg(input + block * 2u + 1u);
+  }
   const float global = *global_scale;
   const uint32_t magnitude = max(max_magnitude(first), max_magnitude(second));
   const float block_max = __uint_as_float(magnitude << 16);
@@ -137,9 +168,10 @@ extern "C" int mircuda_b200_nvfp4_global_scale(const void* input, size_t element
 namespace mircuda_b200 {
 namespace {
 
-template <bool ROW_MAJOR_SCALES>
+template <bool ROW_MAJOR_SCALES, bool SWIGLU = false>
 int launch_quantize(const void* input, const void* global_scale, void* codes, void* scales,
-                    uint32_t rows, uint32_t k, void* stream) {
+                    uint32_t rows, uint32_t k, void* stream,
+                    const unsigned int* row_bound = nullptr) {
   if (input == nullptr || global_scale == nullptr || codes == nullptr || scales == nullptr ||
       stream == nullptr || rows == 0u || k == 0u || k % 64u != 0u) {
     return -1;
@@ -151,10 +183,10 @@ int launch_quantize(const void* input, const void* global_scale, void* codes, vo
   const size_t blocks = static_cast<size_t>(rows) * (k / 16u);
   const size_t grid = (blocks + 255u) / 256u;
   if (grid > 0x7fffffffull) return -1;
-  nvfp4_quantize_kernel<ROW_MAJOR_SCALES>
+  nvfp4_quantize_kernel<ROW_MAJOR_SCALES, SWIGLU>
       <<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
           static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
-          static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, k);
+          static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, row_bound, k);
   return static_cast<int>(cudaPeekAtLastError());
 }
 
@@ -171,4 +203,12 @@ extern "C" int mircuda_b200_nvfp4_quantize_rows_bf16(const void* input, const vo
                                                      void* codes, void* row_scales, uint32_t rows,
                                                      uint32_t k, void* stream) {
   return mircuda_b200::launch_quantize<true>(input, global_scale, codes, row_scales, rows, k, stream);
+}
+
+extern "C" int mircuda_b200_moe_swiglu_nvfp4(const void* input, const void* global_scale,
+                                             void* codes, void* scales, uint32_t rows,
+                                             const unsigned int* row_bound, uint32_t intermediate,
+                                             void* stream) {
+  return mircuda_b200::launch_quantize<false, true>(input, global_scale, codes, scales, rows,
+                                                    intermediate, stream, row_bound);
 }

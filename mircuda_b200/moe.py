@@ -233,6 +233,7 @@ class ExpertParallelMoe:
             self.plan2 = plans.VariableGroupedBf16Plan(stream, plans.VariableGroupedBf16Spec(
                 groups, capacity, hidden, intermediate, rows, self.local_experts))
         self.gemm_events = None   # set to a list to record (name, start, stop) CUDA events
+        self.static_scales = False
 
     # ------------------------------------------------------------------ helpers
     def _handle(self):
@@ -313,14 +314,31 @@ class ExpertParallelMoe:
                 self._p(self.output), self.tokens, self.top_k, self.hidden, handle))
         return self.output
 
-    def calibrate(self, x: torch.Tensor) -> None:
-        """Fixes the activation scale used for rows quantised before dispatch: amax of `x` over
-        all ranks / (448 * 6). Set-up time; call again when the activation range changes."""
+    def calibrate(self, x: torch.Tensor, dispatch: Dispatch | None = None,
+                  routing_weights: torch.Tensor | None = None, margin: float = 2.0) -> None:
+        """Fixes the NVFP4 activation scales at set-up time (call again when the activation range
+        changes). The scale of the dispatched rows is amax of `x` over all ranks / (448 * 6):
+        every rank must use the same value because the plans take one alpha per matrix. When a
+        routing is given, one step is run with the intermediate activations' scale measured
+        from the data; that scale times `margin` is then frozen too, which lets later steps fuse
+        SwiGLU with the quantiser and skip the amax pass."""
         with torch.cuda.stream(self.stream):
             amax = x.abs().max().float().reshape(1)
             if self.world > 1:
                 dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=self.group)
             self.dispatch_global.copy_(torch.where(amax > 0, amax / 2688.0, torch.ones_like(amax)))
+            self.alphas1.copy_((self.weights.gate_up_global * self.dispatch_global).expand_as(self.alphas1))
+        self.static_scales = False
+        if dispatch is None or not self.peer:
+            return
+        self.forward(x, dispatch, routing_weights)
+        with torch.cuda.stream(self.stream):
+            frozen = self.global2 * margin
+            if self.world > 1:
+                dist.all_reduce(frozen, op=dist.ReduceOp.MAX, group=self.group)
+            self.global2.copy_(frozen)
+            self.alphas2.copy_((self.weights.down_global * self.global2).expand_as(self.alphas2))
+        self.static_scales = True
 
     def _forward_peer_fp4(self, x, dispatch: Dispatch, routing_weights):
         lib, handle = self._lib, self._handle()
@@ -331,50 +349,70 @@ class ExpertParallelMoe:
         with torch.cuda.stream(self.stream):
             # Quantise the rank's token rows once (each is dispatched top_k times), scales
             # row-major so that codes and scales travel as rows.
-            plans._check(lib.mircuda_b200_nvfp4_quantize_rows_bf16(
+            self._timed("quantize tokens", lambda: plans._check(lib.mircuda_b200_nvfp4_quantize_rows_bf16(
                 self._p(x), self._p(self.dispatch_global), self._p(self.token_codes),
-                self._p(self.token_scales), self.tokens, self.hidden, handle))
+                self._p(self.token_scales), self.tokens, self.hidden, handle)))
             if self.world > 1:
-                dist.all_gather_into_tensor(self.all_counts, dispatch.counts, group=self.group)
+                self._timed("count exchange", lambda: dist.all_gather_into_tensor(
+                    self.all_counts, dispatch.counts, group=self.group))
                 all_counts = self.all_counts
             else:
                 all_counts = dispatch.counts
-            plans._check(lib.mircuda_b200_moe_expert_layout(
+            self._timed("layout", lambda: plans._check(lib.mircuda_b200_moe_expert_layout(
                 self._p(all_counts), self.world, self.rank, self.experts, 128, self._p(self.base_for_me),
-                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle))
-            for source, pointers, units in ((self.token_codes, self._code_pointers, self._code_units),
-                                            (self.token_scales, self._scale_pointers, self._scale_units)):
-                plans._check(lib.mircuda_b200_moe_dispatch_rows_bf16(
-                    self._p(source), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
-                    self._p(dispatch.position), self._p(self.base_for_me),
-                    ctypes.cast(pointers, pointer_array), self.world, self._p(self.remote_rows),
-                    assignments, self.local_experts, units, handle))
-            if self.world > 1:
-                self._codes_symmetric.barrier()
+                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle)))
+
+            def dispatch_rows():
+                for source, pointers, units in ((self.token_codes, self._code_pointers, self._code_units),
+                                                (self.token_scales, self._scale_pointers, self._scale_units)):
+                    plans._check(lib.mircuda_b200_moe_dispatch_rows_bf16(
+                        self._p(source), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
+                        self._p(dispatch.position), self._p(self.base_for_me),
+                        ctypes.cast(pointers, pointer_array), self.world, self._p(self.remote_rows),
+                        assignments, self.local_experts, units, handle))
+                if self.world > 1:
+                    self._codes_symmetric.barrier()
+
+            self._timed("dispatch", dispatch_rows)
+
             # Row-major scales of the received rows -> 128-row atoms (every expert starts on a
-            # 128-row tile, so the whole buffer is one plain scale matrix).
-            plans._check(lib.mircuda_b200_mxfp8_swizzle_scales(
-                self._p(self.received_scales), self._p(self.scales1), rows, self.hidden // 16, handle))
-            torch.mul(w.gate_up_global, self.dispatch_global, out=self.alphas1[:1])
-            self.alphas1.copy_(self.alphas1[:1].expand_as(self.alphas1))
+            # 128-row tile, so the whole buffer is one plain scale matrix). alphas1 was fixed by
+            # `calibrate`.
+            self._timed("scale atoms", lambda: plans._check(lib.mircuda_b200_moe_scale_atoms(
+                self._p(self.received_scales), self._p(self.scales1), rows, self._p(self.received_rows),
+                self.hidden // 16, handle)))
             self._timed("gate_up", lambda: self.plan1.execute(
                 self.received_codes, self.scales1, w.gate_up_codes, w.gate_up_scales, self.alphas1,
                 self.indices, self.rows, self.offsets, self.offsets, self.hidden_states))
-            plans._check(lib.mircuda_b200_moe_swiglu_bf16(
-                self._p(self.hidden_states), self._p(self.activated), rows, self._p(self.received_rows),
-                self.intermediate, handle))
-            self._quantize(self.activated, rows, self.intermediate, self.global2, self.codes2, self.scales2)
-            torch.mul(w.down_global, self.global2, out=self.alphas2[:1])
-            self.alphas2.copy_(self.alphas2[:1].expand_as(self.alphas2))
+            if self.static_scales:
+                self._timed("swiglu + quantize", lambda: plans._check(lib.mircuda_b200_moe_swiglu_nvfp4(
+                    self._p(self.hidden_states), self._p(self.global2), self._p(self.codes2),
+                    self._p(self.scales2), rows, self._p(self.received_rows), self.intermediate, handle)))
+            else:
+                self._timed("swiglu", lambda: plans._check(lib.mircuda_b200_moe_swiglu_bf16(
+                    self._p(self.hidden_states), self._p(self.activated), rows, self._p(self.received_rows),
+                    self.intermediate, handle)))
+
+                def requantize():
+                    self._quantize(self.activated, rows, self.intermediate, self.global2, self.codes2,
+                                   self.scales2)
+                    torch.mul(w.down_global, self.global2, out=self.alphas2[:1])
+                    self.alphas2.copy_(self.alphas2[:1].expand_as(self.alphas2))
+
+                self._timed("quantize activations", requantize)
             self._timed("down", lambda: self.plan2.execute(
                 self.codes2, self.scales2, w.down_codes, w.down_scales, self.alphas2,
                 self.indices, self.rows, self.offsets, self.offsets, self.expert_out))
-            if self.world > 1:
-                self._result_symmetric.barrier()
-            plans._check(lib.mircuda_b200_moe_collect_rows_bf16(
-                ctypes.cast(self._result_pointers, pointer_array), self.world, self._p(dispatch.slots),
-                self._p(dispatch.sorted_experts), self._p(self.remote_rows), self._p(routing_weights),
-                self._p(self.output), self.tokens, self.top_k, self.local_experts, self.hidden, handle))
+
+            def collect():
+                if self.world > 1:
+                    self._result_symmetric.barrier()
+                plans._check(lib.mircuda_b200_moe_collect_rows_bf16(
+                    ctypes.cast(self._result_pointers, pointer_array), self.world, self._p(dispatch.slots),
+                    self._p(dispatch.sorted_experts), self._p(self.remote_rows), self._p(routing_weights),
+                    self._p(self.output), self.tokens, self.top_k, self.local_experts, self.hidden, handle))
+
+            self._timed("collect", collect)
         return self.output
 
     def _forward_peer(self, x, dispatch: Dispatch, routing_weights):

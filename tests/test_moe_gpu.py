@@ -50,7 +50,7 @@ def run_single(stream, nvfp4, transport="peer"):
     layer = moe.ExpertParallelMoe(stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, TOKENS, capacity, bank,
                                   transport=transport)
     if nvfp4:
-        layer.calibrate(x)
+        layer.calibrate(x, dispatch if transport == "peer" else None, weights)
     torch.cuda.synchronize()
     for _ in range(2):
         out = layer.forward(x, dispatch, weights)
@@ -106,7 +106,7 @@ def _worker(rank, world, port, transport, nvfp4, results):
         layer = moe.ExpertParallelMoe(stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, local_tokens,
                                       capacity, bank, transport=transport)
         if nvfp4:
-            layer.calibrate(x[local])
+            layer.calibrate(x[local], dispatch, weights[local].contiguous())
         torch.cuda.synchronize()
         dist.barrier()
         for _ in range(2):
@@ -135,3 +135,49 @@ def test_moe_layer_expert_parallel_two_gpus(transport, nvfp4):
     assert set(results.keys()) == {0, 1}
     bound = 0.25 if nvfp4 else 5e-3        # NVFP4: plausibility bound, as on one GPU
     assert all(error < bound for error in results.values()), dict(results)
+
+
+def test_fused_swiglu_quantiser_matches_two_passes(cuda_stream):
+    """SwiGLU fused with the NVFP4 quantiser must give the codes and scales of SwiGLU followed by
+    the stand-alone quantiser, bit for bit, and respect the device-side row bound."""
+    import ctypes
+    from mircuda_b200 import _lib
+    library = _lib.load()
+    rows, intermediate, bound_rows = 300, 192, 257
+    generator = torch.Generator(device="cuda").manual_seed(99)
+    hidden = torch.randn(rows, 2 * intermediate, generator=generator, device="cuda").to(torch.bfloat16)
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    handle = ctypes.c_void_p(cuda_stream.cuda_stream)
+    activated = torch.zeros(rows, intermediate, dtype=torch.bfloat16, device="cuda")
+    global_scale = torch.full((1,), 0.0031, dtype=torch.float32, device="cuda")
+    scale_bytes = (rows + 127) // 128 * (intermediate // 64) * 512
+    codes = [torch.zeros(rows * intermediate // 2, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    scales = [torch.zeros(scale_bytes, dtype=torch.uint8, device="cuda") for _ in range(2)]
+    bound = torch.tensor([bound_rows], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    assert library.mircuda_b200_moe_swiglu_bf16(p(hidden), p(activated), rows, p(bound), intermediate, handle) == 0
+    assert library.mircuda_b200_nvfp4_quantize_bf16(p(activated), p(global_scale), p(codes[0]), p(scales[0]),
+                                                    bound_rows, intermediate, handle) == 0
+    assert library.mircuda_b200_moe_swiglu_nvfp4(p(hidden), p(global_scale), p(codes[1]), p(scales[1]), rows,
+                                                 p(bound), intermediate, handle) == 0
+    cuda_stream.synchronize()
+    assert torch.equal(codes[0], codes[1]) and torch.equal(scales[0], scales[1])
+    assert codes[1][bound_rows * intermediate // 2:].eq(0).all() and codes[1].any()
+
+
+def test_scale_atoms_matches_swizzle(cuda_stream):
+    import ctypes
+    from mircuda_b200 import _lib
+    library = _lib.load()
+    rows, columns = 300, 128
+    source = torch.randint(0, 256, (rows * columns,), dtype=torch.uint8, device="cuda")
+    size = (rows + 127) // 128 * 128 * columns
+    expected = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    actual = torch.zeros(size, dtype=torch.uint8, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())
+    handle = ctypes.c_void_p(cuda_stream.cuda_stream)
+    torch.cuda.synchronize()
+    assert library.mircuda_b200_mxfp8_swizzle_scales(p(source), p(expected), rows, columns, handle) == 0
+    assert library.mircuda_b200_moe_scale_atoms(p(source), p(actual), rows, None, columns, handle) == 0
+    cuda_stream.synchronize()
+    assert torch.equal(actual, expected)
