@@ -93,14 +93,18 @@ marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
     }
 
     __syncthreads();   // the previous round's activations are no longer needed
-    const int round_k = round_tiles * kTileK;
-    for (int index = threadIdx.x; index < kRows * round_k; index += kThreads) {
-      const int row = index / round_k;
-      const int column = index % round_k;
-      const int source = (first_tile_k + round_tile) * kTileK + column;
-      __nv_bfloat16 value = __float2bfloat16_rn(0.0f);
-      if (row < tokens) value = input[static_cast<size_t>(row) * k + source];
-      shared_x[row * x_stride + column] = value;
+    // Activations of the round: 16-byte pieces (a K tile is two of them; k % 16 == 0 keeps
+    // every piece aligned in global memory, the row stride of shared_x is a multiple of 8).
+    const int round_pieces = round_tiles * 2;
+    for (int index = threadIdx.x; index < kRows * round_pieces; index += kThreads) {
+      const int row = index / round_pieces;
+      const int piece = index - row * round_pieces;
+      uint4 value = make_uint4(0u, 0u, 0u, 0u);
+      if (row < tokens) {
+        value = __ldg(reinterpret_cast<const uint4*>(
+                          input + static_cast<size_t>(row) * k + (first_tile_k + round_tile) * kTileK) + piece);
+      }
+      *reinterpret_cast<uint4*>(shared_x + row * x_stride + piece * 8) = value;
     }
     __syncthreads();
 
@@ -217,7 +221,8 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
   if (stream == nullptr || input == nullptr || weight == nullptr || output == nullptr ||
       temporary == nullptr || scales == nullptr || global_scale == nullptr || locks == nullptr ||
       tokens <= 0 || tokens > kMaxTokens || output_features <= 0 || input_features <= 0 ||
-      output_features % kTileN != 0 || input_features % kTileK != 0) {
+      output_features % kTileN != 0 || input_features % kTileK != 0 ||
+      (reinterpret_cast<uintptr_t>(input) & 15u) != 0u) {
     return -1;
   }
   int device = 0, sm_count = 0;

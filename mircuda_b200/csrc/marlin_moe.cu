@@ -107,16 +107,18 @@ marlin_moe_kernel(const __nv_bfloat16* __restrict__ input, const uint4* __restri
     }
 
     __syncthreads();   // ids are visible; the previous round's activations are no longer needed
-    const int round_k = round_tiles * kTileK;
-    for (int index = threadIdx.x; index < kRows * round_k; index += kThreads) {
-      const int row = index / round_k;
-      const int column = index % round_k;
+    // Activations of the round in 16-byte pieces (a K tile is two of them).
+    const int round_pieces = round_tiles * 2;
+    for (int index = threadIdx.x; index < kRows * round_pieces; index += kThreads) {
+      const int row = index / round_pieces;
+      const int piece = index - row * round_pieces;
       const int id = ids[row];
-      __nv_bfloat16 value = __float2bfloat16_rn(0.0f);
+      uint4 value = make_uint4(0u, 0u, 0u, 0u);
       if (id < assignments) {
-        value = input[static_cast<size_t>(id / top_k) * k + round_tile * kTileK + column];
+        value = __ldg(reinterpret_cast<const uint4*>(
+                          input + static_cast<size_t>(id / top_k) * k + round_tile * kTileK) + piece);
       }
-      shared_x[row * x_stride + column] = value;
+      *reinterpret_cast<uint4*>(shared_x + row * x_stride + piece * 8) = value;
     }
     __syncthreads();
 
@@ -202,7 +204,7 @@ int execute(void* stream, const void* input, const void* weight, void* output, c
       scales == nullptr || sorted == nullptr || expert_ids == nullptr || padded == nullptr ||
       routing == nullptr || (!MXFP4 && global_scales == nullptr) || top_k <= 0 || tokens <= 0 ||
       n <= 0 || k <= 0 || n % kTileN != 0 || k % (MXFP4 ? 32 : kTileK) != 0 || thread_config < 0 ||
-      thread_config > 5) {
+      thread_config > 5 || (reinterpret_cast<uintptr_t>(input) & 15u) != 0u) {
     return -1;
   }
   // Thread configurations 0-2 route in blocks of 8 rows, 3-5 in blocks of 64
