@@ -340,6 +340,24 @@ int mircuda_fp8_vector_execute(void* plan, void* stream, const void* input,
                                const void* weight_scales, void* output);
 void mircuda_fp8_vector_destroy(void* plan);
 
+/* ------------------------------- FP8 matmul with token / channel scales and bias ----
+ * y[m, n] = bf16(input_scales[m] * (weight_scale * sum_k e4m3(x[m, k]) * e4m3(w[n, k])) + bias[n]),
+ * fp32 accumulation; the product with the weight scale is rounded to fp32 first, the rest is
+ * one fma (one multiply without a bias). input_scales: m fp32. weight_scales: fp32
+ * (scale_type 0) or bf16 (1); one value (weight_scale_type 0) or n (1). bias: n bf16, or null
+ * when has_bias == 0. n % 16 == 0, k % 16 == 0. tile (0 or 1) selects between the reference's
+ * two decode tile shapes; it is validated and otherwise has no meaning here. m <= 16 streams
+ * the weights through mma.sync e4m3; larger m runs tcgen05 kind::f8f6f4.
+ * Replaces sys/native/scaled_fp8_sm120.cu:125-206, declared in
+ * sys/src/platform/cutlass/scaled_fp8.rs:11-36. workspace_bytes is always 0. */
+int mircuda_scaled_fp8_create(int m, int n, int k, int scale_type, int weight_scale_type,
+                              int has_bias, int tile, void* stream, void** output);
+size_t mircuda_scaled_fp8_workspace_bytes(const void* plan);
+int mircuda_scaled_fp8_execute(void* plan, void* stream, const void* input, const void* weight,
+                               const float* input_scales, const void* weight_scales,
+                               const void* bias, void* output);
+void mircuda_scaled_fp8_destroy(void* plan);
+
 /* ------------------------------------------------------------- dense f16 / bf16 GEMM ----
  * C[m, n] = alpha * A[m, k] . B[n, k]^T + beta * C; input_type 0 = f16, 1 = bf16; output_type
  * = input_type or 2 (f32). Any shape: k and n multiples of 8 run on tcgen05, others on a

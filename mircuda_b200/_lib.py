@@ -76,6 +76,10 @@ SIGNATURES.update({
     "mircuda_fp8_vector_workspace_bytes": (_sz, [_vp]),
     "mircuda_fp8_vector_execute": (_i, [_vp] * 7),
     "mircuda_fp8_vector_destroy": (None, [_vp]),
+    "mircuda_scaled_fp8_create": (_i, [_i] * 7 + [_vp, _vpp]),
+    "mircuda_scaled_fp8_workspace_bytes": (_sz, [_vp]),
+    "mircuda_scaled_fp8_execute": (_i, [_vp] * 8),
+    "mircuda_scaled_fp8_destroy": (None, [_vp]),
     "mircuda_dense_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_dense_workspace_bytes": (_sz, [_vp]),
     "mircuda_dense_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _f, _f]),

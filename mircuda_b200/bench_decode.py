@@ -1,6 +1,6 @@
 """Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
 
-    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16]
+    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8]
 
 Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
 examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
@@ -160,6 +160,25 @@ def bench_w4a16(stream, n, k, m, cycles, repeats):
     return seconds, n * k * 0.5 + n * k / 128 * 2 + m * k * 2 + m * n * 2, banks
 
 
+def bench_scaled_fp8(stream, n, k, m, cycles, repeats):
+    """E4M3 weights and activations, fp32 token scales, fp32 channel scales, bf16 bias."""
+    from . import dense
+    banks = _banks(n * k)
+    weights = [_random_bytes(n * k, 0x20, 0x48) for _ in range(banks)]
+    x = _random_bytes(m * k, 0x20, 0x48)
+    token_scales = torch.rand(m, device="cuda") + 0.5
+    channel_scales = torch.rand(n, device="cuda") * 0.04 + 0.01
+    bias = torch.randn(n, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    plan = dense.ScaledFp8Plan(stream, dense.ScaledFp8Spec(m, k, n, torch.float32, "output_channel", True))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute_f32_scales(stream, x, weights[i], token_scales,
+                                                              channel_scales, bias, out),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, n * k + m * k + m * n * 2 + n * 6 + m * 4, banks
+
+
 def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None) -> dict:
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
@@ -168,7 +187,8 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
         for name, n, k in (W4A16_SHAPES if op == "w4a16" else SHAPES):
             if shapes and name not in shapes:
                 continue
-            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else [1]):
+            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else
+                      [1, 16, 512] if op == "scaled_fp8" else [1]):
                 if tokens and m not in tokens:
                     continue
                 with torch.cuda.stream(stream):
@@ -180,13 +200,15 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                         seconds, byte_count, banks = bench_dense(stream, n, k, cycles, repeats)
                     elif op == "w4a16":
                         seconds, byte_count, banks = bench_w4a16(stream, n, k, m, cycles, repeats)
+                    elif op == "scaled_fp8":
+                        seconds, byte_count, banks = bench_scaled_fp8(stream, n, k, m, cycles, repeats)
                     else:
                         seconds, byte_count, banks = bench_marlin(stream, n, k, m, cycles, repeats)
                 torch.cuda.empty_cache()
                 record = {"op": op, "shape": name, "n": n, "k": k, "m": m, "us": seconds * 1e6,
                           "gbs": byte_count / seconds / 1e9, "frac_of_measured_hbm":
                           byte_count / seconds / 1e9 / peak_gbs, "banks": banks}
-                if op == "w4a16":
+                if op in ("w4a16", "scaled_fp8"):
                     record["tflops"] = 2.0 * m * n * k / seconds / 1e12
                 results.append(record)
                 print(json.dumps(record), flush=True)

@@ -332,4 +332,19 @@ __device__ __forceinline__ void mma_f16(uint32_t d_tmem, uint64_t a_descriptor,
       : "memory");
 }
 
+// kind::f8f6f4 without block scales: one-byte operands (here e4m3, format 0 in the descriptor
+// built by make_f16_idesc(false, m, n)), fp32 accumulator, 32 bytes of K per instruction.
+__device__ __forceinline__ void mma_f8f6f4(uint32_t d_tmem, uint64_t a_descriptor,
+                                           uint64_t b_descriptor, uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem),
+      "l"(a_descriptor), "l"(b_descriptor), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+
 }  // namespace mircuda_b200::ptx

@@ -179,3 +179,86 @@ class BlockwiseFp8VectorPlan:
             self._raw = None
 
     __del__ = close
+
+
+@dataclass(frozen=True)
+class ScaledFp8Spec:
+    """``ScaledFp8Spec`` (src/cutlass/scaled_fp8.rs:29-87): E4M3 [tokens, input_features] x E4M3
+    [output_features, input_features] with one fp32 scale per token, one weight scale for the
+    tensor (``weight_scale="tensor"``) or per output channel (``"output_channel"``) in fp32 or
+    bf16 (``scale``), and an optional bf16 bias. Both feature counts are multiples of 16.
+    ``tile`` (0 or 1) is the reference's decode-tile choice; it has no meaning here."""
+    tokens: int
+    input_features: int
+    output_features: int
+    scale: torch.dtype = torch.float32
+    weight_scale: str = "tensor"
+    has_bias: bool = False
+    tile: int = 0
+
+    def __post_init__(self):
+        if (self.tokens <= 0 or self.input_features <= 0 or self.output_features <= 0
+                or self.input_features % 16 != 0 or self.output_features % 16 != 0):
+            raise InvalidMatmulShape("feature counts must be positive multiples of 16")
+        if self.scale not in (torch.float32, torch.bfloat16):
+            raise InvalidMatmulShape("weight scales are fp32 or bf16")
+        if self.weight_scale not in ("tensor", "output_channel") or self.tile not in (0, 1):
+            raise InvalidMatmulShape("unknown weight scale geometry or tile")
+
+    def weight_scale_elements(self) -> int:
+        return 1 if self.weight_scale == "tensor" else self.output_features
+
+
+class ScaledFp8Plan:
+    """``ScaledFp8Plan`` over ``mircuda_scaled_fp8_*``."""
+
+    def __init__(self, stream, spec: ScaledFp8Spec):
+        self._lib = _lib.load()
+        self.spec, self._stream = spec, stream
+        raw = ctypes.c_void_p()
+        _check(self._lib.mircuda_scaled_fp8_create(
+            spec.tokens, spec.output_features, spec.input_features,
+            0 if spec.scale == torch.float32 else 1, 0 if spec.weight_scale == "tensor" else 1,
+            int(spec.has_bias), spec.tile, _stream_handle(stream), ctypes.byref(raw)))
+        self._raw = raw
+
+    def workspace_bytes(self) -> int:
+        return int(self._lib.mircuda_scaled_fp8_workspace_bytes(self._raw))
+
+    def execute_f32_scales(self, stream, input, weight, input_scales, weight_scales, bias, output):
+        if self.spec.scale != torch.float32:
+            raise InvalidMatmulShape("plan was built for bf16 weight scales")
+        self._execute(stream, input, weight, input_scales, weight_scales, bias, output)
+
+    def execute_bf16_scales(self, stream, input, weight, input_scales, weight_scales, bias, output):
+        if self.spec.scale != torch.bfloat16:
+            raise InvalidMatmulShape("plan was built for fp32 weight scales")
+        self._execute(stream, input, weight, input_scales, weight_scales, bias, output)
+
+    def _execute(self, stream, input, weight, input_scales, weight_scales, bias, output) -> None:
+        if stream.cuda_stream != self._stream.cuda_stream:
+            raise StreamMismatch()
+        s = self.spec
+        if (bias is not None) != s.has_bias:
+            raise InvalidMatmulShape("bias does not match the plan")
+        _exact("input", s.tokens * s.input_features, input)
+        _exact("weight", s.output_features * s.input_features, weight)
+        _exact("input scales", s.tokens, input_scales)
+        _exact("weight scales", s.weight_scale_elements(), weight_scales)
+        _exact("output", s.tokens * s.output_features, output)
+        if bias is not None:
+            _exact("bias", s.output_features, bias)
+        bytes_ = (torch.uint8, torch.int8)
+        _check(self._lib.mircuda_scaled_fp8_execute(
+            self._raw, _stream_handle(stream), _device_pointer(input, bytes_),
+            _device_pointer(weight, bytes_), _device_pointer(input_scales, (torch.float32,)),
+            _device_pointer(weight_scales, (s.scale,)),
+            None if bias is None else _device_pointer(bias, (torch.bfloat16,)),
+            _device_pointer(output, (torch.bfloat16,))))
+
+    def close(self) -> None:
+        if getattr(self, "_raw", None):
+            self._lib.mircuda_scaled_fp8_destroy(self._raw)
+            self._raw = None
+
+    __del__ = close

@@ -418,6 +418,26 @@ def indexed_grouped_fp4(a, a_scales, b, b_scales, alphas, selected, c_bits, expe
     return output
 
 
+def scaled_fp8(x_codes, w_codes, input_scales, weight_scales, bias_bits, m: int, n: int,
+               k: int) -> np.ndarray:
+    """FP8 matmul with epilogue scales (sys/native/scaled_fp8_sm120.cuh:21-50): the fp32
+    accumulator is multiplied by the weight scale (one value, or one per output channel; fp32
+    or bf16 already widened to fp32 by the caller) and rounded to fp32, then multiplied by the
+    token's fp32 scale and, with a bias, added to the bf16 bias in one fused multiply-add,
+    and rounded to bf16. Returns bf16 bits [m, n]."""
+    table = e4m3_table().astype(np.float64)
+    x = table[_c(x_codes, np.uint8).reshape(m, k)]
+    w = table[_c(w_codes, np.uint8).reshape(n, k)]
+    accumulator = (x @ w.T).astype(np.float32)
+    channel = np.broadcast_to(_c(weight_scales, np.float32).reshape(1, -1), (1, n))
+    scaled = (channel * accumulator).astype(np.float32)
+    tokens = _c(input_scales, np.float32).reshape(m, 1).astype(np.float64)
+    result = tokens * scaled.astype(np.float64)          # exact in f64: two 24-bit factors
+    if bias_bits is not None:
+        result = result + bf16_to_f32(bias_bits).reshape(1, n).astype(np.float64)
+    return f32_to_bf16(result.astype(np.float32))
+
+
 def compare_bf16(actual_bits, expected_bits) -> dict:
     """max|d|/max|ref| and relative Frobenius error between two bf16 bit arrays."""
     actual = bf16_to_f32(np.asarray(actual_bits).reshape(-1)).astype(np.float64)

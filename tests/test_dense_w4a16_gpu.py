@@ -159,3 +159,67 @@ def test_fp8_vector_random(cuda_stream):
     cuda_stream.synchronize()
     plan.close()
     assert_close(out, torch.from_numpy(expected), "blockwise fp8 vector")
+
+
+def _run_scaled_fp8(cuda_stream, m, n, k, x, w, sa, sb, bias, scale_dtype, tile=0):
+    from mircuda_b200 import dense
+    spec = dense.ScaledFp8Spec(m, k, n, scale_dtype, "tensor" if len(sb) == 1 else "output_channel",
+                               bias is not None, tile)
+    out = torch.zeros(m * n, dtype=torch.bfloat16, device="cuda")
+    device_bias = None if bias is None else torch.from_numpy(bias.view(np.int16)).view(torch.bfloat16).cuda()
+    device_sb = torch.from_numpy(sb).cuda().to(scale_dtype)
+    operands = (torch.from_numpy(x.reshape(-1)).cuda(), torch.from_numpy(w.reshape(-1)).cuda(),
+                torch.from_numpy(sa).cuda(), device_sb, device_bias, out)
+    plan = dense.ScaledFp8Plan(cuda_stream, spec)
+    assert plan.workspace_bytes() == 0
+    torch.cuda.synchronize()
+    execute = plan.execute_f32_scales if scale_dtype == torch.float32 else plan.execute_bf16_scales
+    for _ in range(2):
+        execute(cuda_stream, *operands)
+    cuda_stream.synchronize()
+    plan.close()
+    return out.view(m, n), device_sb.float().cpu().numpy()
+
+
+@pytest.mark.parametrize("tile", [0, 1])
+def test_scaled_fp8_goldens(cuda_stream, tile):
+    """tests/cutlass/scaled_fp8.rs:9-71: both of the reference's cases, bit for bit."""
+    ones_x = np.full(16, 0x38, dtype=np.uint8)
+    ones_w = np.full(256, 0x38, dtype=np.uint8)
+    channel = np.arange(1, 17, dtype=np.float32) / 16.0
+    import oracle
+    bias = oracle.f32_to_bf16(np.ones(16, dtype=np.float32))
+    out, _ = _run_scaled_fp8(cuda_stream, 1, 16, 16, ones_x, ones_w, np.float32([0.5]), channel, bias,
+                             torch.float32, tile)
+    assert (out.float().cpu().numpy().reshape(-1) == (8.0 * channel + 1.0).astype(np.float32)).all()
+    out, _ = _run_scaled_fp8(cuda_stream, 1, 16, 16, ones_x, ones_w, np.float32([0.5]),
+                             np.float32([0.25]), None, torch.float32, tile)
+    assert (out.float() == 2.0).all()
+
+
+@pytest.mark.parametrize("m,n,k,channel,with_bias,scale_dtype", [
+    (1, 1024, 4096, True, True, torch.float32),
+    (5, 48, 80, True, False, torch.bfloat16),         # ragged K (not a multiple of 64), small N
+    (8, 2048, 1040, False, True, torch.float32),
+    (13, 512, 2048, True, True, torch.bfloat16),      # second token half, partly filled
+    (16, 1024, 4096, False, False, torch.float32),
+    (17, 272, 144, True, True, torch.float32),        # tcgen05 path: ragged M, N, K tiles
+    (200, 1024, 1024, True, True, torch.bfloat16),
+    (512, 2048, 4096, False, False, torch.float32),
+])
+def test_scaled_fp8_random(cuda_stream, m, n, k, channel, with_bias, scale_dtype):
+    import oracle
+    rng = np.random.default_rng(m * 7919 + n + k)
+    x = rng.integers(0, 256, size=(m, k), dtype=np.uint8)
+    w = rng.integers(0, 256, size=(n, k), dtype=np.uint8)
+    # No NaN codes, and magnitudes kept below 2^4 so that sums stay far inside fp32 / bf16 range.
+    for codes in (x, w):
+        codes[(codes & 0x7F) >= 0x60] &= 0x9F
+    sa = rng.uniform(0.5, 2.0, size=m).astype(np.float32)
+    sb = rng.uniform(0.01, 0.05, size=n if channel else 1).astype(np.float32)
+    bias = oracle.f32_to_bf16(rng.normal(0, 2.0, size=n).astype(np.float32)) if with_bias else None
+    out, used_sb = _run_scaled_fp8(cuda_stream, m, n, k, x, w, sa, sb, bias, scale_dtype)
+    expected = oracle.scaled_fp8(x, w, sa, used_sb, bias, m, n, k)
+    actual = out.view(torch.int16).cpu().numpy().view(np.uint16)
+    stats = oracle.compare_bf16(actual, expected)
+    assert stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3, stats

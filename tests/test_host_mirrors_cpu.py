@@ -79,6 +79,10 @@ def test_new_entry_points_validate_without_a_gpu(library):
     assert library.mircuda_b200_mxfp8_bf16_gathered(None, None, None, None, None, None, 1, 1, 1, 32, 1, fake) == -1
     assert library.mircuda_marlin_nvfp4_moe_execute(fake, None, None, None, None, None, None, None, None,
                                                     None, None, 1, False, 1, 64, 64, 0, None, False) == -1
+    assert library.mircuda_scaled_fp8_create(1, 24, 16, 0, 0, 0, 0, fake, ctypes.byref(raw)) == -1   # n % 16
+    assert library.mircuda_scaled_fp8_create(1, 16, 16, 2, 0, 0, 0, fake, ctypes.byref(raw)) == -1   # scale type
+    assert library.mircuda_scaled_fp8_create(1, 16, 16, 0, 0, 0, 2, fake, ctypes.byref(raw)) == -1   # tile
+    assert library.mircuda_scaled_fp8_workspace_bytes(None) == 0
     assert library.mircuda_dense_workspace_bytes(None) == 0
     assert library.mircuda_fp8_vector_workspace_bytes(None) == 0
     library.mircuda_variable_grouped_fp4_destroy(None)
@@ -86,3 +90,19 @@ def test_new_entry_points_validate_without_a_gpu(library):
     library.mircuda_dense_destroy(None)
     library.mircuda_b200_w4a16_destroy(None)
     library.mircuda_fp8_vector_destroy(None)
+    library.mircuda_scaled_fp8_destroy(None)
+
+
+def test_scaled_fp8_spec_validation():
+    import torch
+    from mircuda_b200 import dense, plans
+    spec = dense.ScaledFp8Spec(3, 32, 48, torch.bfloat16, "output_channel", True)
+    assert spec.weight_scale_elements() == 48
+    assert dense.ScaledFp8Spec(1, 16, 16).weight_scale_elements() == 1
+    for bad in ((0, 16, 16), (1, 24, 16), (1, 16, 8)):
+        with pytest.raises(plans.InvalidMatmulShape):
+            dense.ScaledFp8Spec(*bad)
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.ScaledFp8Spec(1, 16, 16, torch.float16)
+    with pytest.raises(plans.InvalidMatmulShape):
+        dense.ScaledFp8Spec(1, 16, 16, torch.float32, "row")

@@ -230,3 +230,18 @@ def test_indexed_grouped_fp4_golden_rows():
     out = oracle.indexed_grouped_fp4(a, a_scales, weights, bank_scales, alphas, [0, 1],
                                      np.full((4, n), 0x3F80, np.uint16), matrices, 2, n, k, True)
     assert oracle.bf16_to_f32(out)[:, 0].tolist() == [0.0, 0.0, 128.0, 128.0]
+
+
+def test_scaled_fp8_golden():
+    """per_token_and_channel_scales_with_bias and per_token_and_tensor_scale
+    (tests/cutlass/scaled_fp8.rs:9-71): ones, token scale 0.5, channel scales j/16 and bias 1
+    -> 8 * j/16 + 1; tensor scale 0.25 -> 2."""
+    ones_x = np.full(16, 0x38, dtype=np.uint8)
+    ones_w = np.full(256, 0x38, dtype=np.uint8)
+    channel = np.arange(1, 17, dtype=np.float32) / 16.0
+    bias = oracle.f32_to_bf16(np.ones(16, dtype=np.float32))
+    out = oracle.scaled_fp8(ones_x, ones_w, [0.5], channel, bias, 1, 16, 16)
+    expected = oracle.f32_to_bf16((8.0 * channel + 1.0).astype(np.float32))
+    assert (out.reshape(-1) == expected).all()
+    out = oracle.scaled_fp8(ones_x, ones_w, [0.5], [0.25], None, 1, 16, 16)
+    assert (oracle.bf16_to_f32(out) == 2.0).all()
