@@ -1,6 +1,6 @@
 """Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
 
-    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8]
+    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8,marlin_moe]
 
 Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
 examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
@@ -160,6 +160,59 @@ def bench_w4a16(stream, n, k, m, cycles, repeats):
     return seconds, n * k * 0.5 + n * k / 128 * 2 + m * k * 2 + m * n * 2, banks
 
 
+MARLIN_MOE_SHAPES = [("moe_gate_up", 1536, 2048), ("moe_down", 2048, 768)]
+MOE_EXPERTS, MOE_TOP_K = 128, 8
+
+
+def bench_marlin_moe(stream, n, k, m, cycles, repeats):
+    """Routed Marlin NVFP4 projection, 128 experts, 8 choices per token (Qwen3-30B-A3B sizes).
+    Sixteen route sets are rotated so that consecutive launches touch different experts; the
+    byte count is the weights of the experts a launch touches plus its rows in and out."""
+    library = _lib.load()
+    experts, top_k, block = MOE_EXPERTS, MOE_TOP_K, 8
+    weights = _random_bytes(experts * n * k // 2, 0, 256)
+    scales = _random_bytes(experts * n * k // 16, 0x90, 0xF0)          # prepared codes
+    global_scales = torch.full((experts,), 2.0 ** 100, dtype=torch.float32, device="cuda")
+    x = torch.randn(m * k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m * top_k * n, dtype=torch.bfloat16, device="cuda")
+    handle = ctypes.c_void_p(stream.cuda_stream)
+    pointer = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    assignments = m * top_k
+    capacity = assignments + experts * (block - 1)
+    routes, touched = [], 0.0
+    for rotation in range(16):
+        token, choice = torch.arange(m).view(-1, 1), torch.arange(top_k).view(1, -1)
+        selected = ((rotation + 16 * choice + 3 * token) % experts).to(torch.int32).reshape(-1)
+        touched += len(torch.unique(selected)) / 16.0
+        buffers = dict(selected=selected.cuda(),
+                       routing=torch.ones(assignments, dtype=torch.bfloat16, device="cuda"),
+                       sorted=torch.zeros(capacity, dtype=torch.int32, device="cuda"),
+                       expert_ids=torch.zeros((capacity + block - 1) // block, dtype=torch.int32, device="cuda"),
+                       padded=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                       offsets=torch.zeros(experts, dtype=torch.int32, device="cuda"),
+                       routing_f32=torch.zeros(assignments, dtype=torch.float32, device="cuda"))
+        status = library.mircuda_marlin_prepare_moe_routes(
+            handle, pointer(buffers["selected"]), pointer(buffers["routing"]), pointer(buffers["sorted"]),
+            pointer(buffers["expert_ids"]), pointer(buffers["padded"]), pointer(buffers["offsets"]),
+            pointer(buffers["routing_f32"]), assignments, experts, block)
+        if status != 0:
+            raise RuntimeError(f"marlin route preparation status {status}")
+        routes.append(buffers)
+    torch.cuda.synchronize()
+
+    def launch(index):
+        route = routes[index]
+        status = library.mircuda_marlin_nvfp4_moe_execute(
+            handle, pointer(x), pointer(weights), pointer(out), None, pointer(scales),
+            pointer(global_scales), pointer(route["sorted"]), pointer(route["expert_ids"]),
+            pointer(route["padded"]), pointer(route["routing_f32"]), top_k, False, m, n, k, 0, None, False)
+        if status != 0:
+            raise RuntimeError(f"marlin moe status {status}")
+
+    seconds = _time(stream, launch, len(routes), cycles, repeats)
+    return seconds, touched * n * k * 0.5625 + m * k * 2 + assignments * n * 2, len(routes)
+
+
 def bench_scaled_fp8(stream, n, k, m, cycles, repeats):
     """E4M3 weights and activations, fp32 token scales, fp32 channel scales, bf16 bias."""
     from . import dense
@@ -184,11 +237,13 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
     stream = torch.cuda.Stream()
     results = []
     for op in ops:
-        for name, n, k in (W4A16_SHAPES if op == "w4a16" else SHAPES):
+        for name, n, k in (W4A16_SHAPES if op == "w4a16" else MARLIN_MOE_SHAPES if op == "marlin_moe"
+                           else SHAPES):
             if shapes and name not in shapes:
                 continue
             for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else
-                      [1, 16, 512] if op == "scaled_fp8" else [1]):
+                      [1, 16, 512] if op == "scaled_fp8" else
+                      [1, 8, 64] if op == "marlin_moe" else [1]):
                 if tokens and m not in tokens:
                     continue
                 with torch.cuda.stream(stream):
@@ -200,6 +255,8 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                         seconds, byte_count, banks = bench_dense(stream, n, k, cycles, repeats)
                     elif op == "w4a16":
                         seconds, byte_count, banks = bench_w4a16(stream, n, k, m, cycles, repeats)
+                    elif op == "marlin_moe":
+                        seconds, byte_count, banks = bench_marlin_moe(stream, n, k, m, cycles, repeats)
                     elif op == "scaled_fp8":
                         seconds, byte_count, banks = bench_scaled_fp8(stream, n, k, m, cycles, repeats)
                     else:
