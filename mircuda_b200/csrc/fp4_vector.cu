@@ -22,7 +22,11 @@
 #include <mutex>
 #include <new>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "fp4_codec.cuh"
+#include "fp4_vector_tc.hpp"
 #include "ptx.cuh"
 #include "layout.cuh"
 
@@ -43,6 +47,7 @@ struct Plan {
   cudaStream_t stream;
   float* partials;          // [slices][row_tiles * 128]
   unsigned int* counters;   // [row_tiles], zero between launches
+  fp4_vector_tc::Plan* tensor;   // the tensor-core implementation, when the plan uses it
 };
 
 __global__ void __launch_bounds__(kThreads)
@@ -170,6 +175,24 @@ extern "C" int mircuda_fp4_vector_create(int n, int k, void* stream, void** outp
   plan->k = k;
   plan->slices = (k + kTileK - 1) / kTileK;
   plan->stream = static_cast<cudaStream_t>(stream);
+  // Two implementations. The tensor-core kernel (fp4_vector_tc.cu) streams faster but pays
+  // about 2 us more per launch (tensor-memory allocation, pipeline fill, hand-over of K parts
+  // through global memory); measured on B200 it wins from about 24 MB of weights up (0.59 of
+  // HBM speed against 0.48 at 24576 x 4096, 0.17 against 0.22 at 4096 x 4096).
+  // MIRCUDA_B200_FP4_VECTOR=tensor or =simt overrides the choice.
+  const char* choice = std::getenv("MIRCUDA_B200_FP4_VECTOR");
+  bool tensor = static_cast<size_t>(n) * static_cast<size_t>(k) / 2u >= (size_t{24} << 20);
+  if (choice != nullptr && std::strcmp(choice, "tensor") == 0) tensor = true;
+  if (choice != nullptr && std::strcmp(choice, "simt") == 0) tensor = false;
+  if (tensor) {
+    const int status = mircuda_b200::fp4_vector_tc::create(n, k, plan->stream, &plan->tensor);
+    if (status != 0) {
+      delete plan;
+      return status;
+    }
+    *output = plan;
+    return 0;
+  }
   const size_t row_tiles = (static_cast<size_t>(n) + kTileRows - 1) / kTileRows;
   int status = 0;
   if (plan->slices > 1) {
@@ -210,6 +233,11 @@ extern "C" int mircuda_fp4_vector_execute(void* raw, void* stream, const void* i
         reinterpret_cast<uintptr_t>(weight_scales)) & 15u) != 0u) {
     return -1;
   }
+  if (plan->tensor != nullptr) {
+    if ((reinterpret_cast<uintptr_t>(input_scales) & 15u) != 0u) return -1;
+    return mircuda_b200::fp4_vector_tc::execute(plan->tensor, cuda_stream, input, input_scales, weight,
+                                                weight_scales, output, alpha);
+  }
   const dim3 grid((plan->n + kTileRows - 1) / kTileRows, plan->slices);
   fp4_vector_kernel<<<grid, kThreads, 0, cuda_stream>>>(
       static_cast<const uint8_t*>(input), static_cast<const uint8_t*>(input_scales),
@@ -222,6 +250,7 @@ extern "C" int mircuda_fp4_vector_execute(void* raw, void* stream, const void* i
 extern "C" void mircuda_fp4_vector_destroy(void* raw) {
   auto* plan = static_cast<mircuda_b200::fp4_vector::Plan*>(raw);
   if (plan == nullptr) return;
+  mircuda_b200::fp4_vector_tc::destroy(plan->tensor);
   if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
   if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
   delete plan;

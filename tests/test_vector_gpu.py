@@ -73,7 +73,15 @@ def run_fp4_vector(stream, x, xs, w, ws, n, k, alpha):
     return bf16_bits(out)
 
 
-def test_fp4_vector_golden(cuda_stream):
+@pytest.fixture(params=["tensor", "simt"])
+def fp4_vector_kernel(request, monkeypatch):
+    """Both implementations behind mircuda_fp4_vector_*: the tcgen05 kernel (chosen for large
+    weights) and the CUDA-core kernel; the override is read when a plan is created."""
+    monkeypatch.setenv("MIRCUDA_B200_FP4_VECTOR", request.param)
+    return request.param
+
+
+def test_fp4_vector_golden(cuda_stream, fp4_vector_kernel):
     """tests/cutlass/fp4/vector.rs:11-30 — all 0x22 / 0x38, N=704, K=2816 -> 2816.0."""
     n, k = 704, 2816
     x = np.full(k // 2, 0x22, np.uint8)
@@ -84,8 +92,9 @@ def test_fp4_vector_golden(cuda_stream):
     assert (oracle.bf16_to_f32(out) == 2816.0).all()
 
 
-@pytest.mark.parametrize("n,k", [(4096, 4096), (200, 448), (129, 64), (2048, 2816)])
-def test_fp4_vector_random(cuda_stream, n, k):
+@pytest.mark.parametrize("n,k", [(4096, 4096), (200, 448), (129, 64), (2048, 2816), (24576, 4096),
+                                 (4096, 12288), (128, 192)])
+def test_fp4_vector_random(cuda_stream, fp4_vector_kernel, n, k):
     x, xs = random_fp4(1, k, 11)
     w, ws = random_fp4(n, k, 12)
     expected = oracle.fp4_vector(x, xs, w, ws, n, k, 0.5)
