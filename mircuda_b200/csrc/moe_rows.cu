@@ -68,7 +68,7 @@ moe_swiglu_kernel(const uint4* __restrict__ input, uint4* __restrict__ output, u
     for (int word = 0; word < 4; ++word) {
       const float2 g = unpack(gates[word]);
       const float2 u = unpack(ups[word]);
-      packed[word] = pack(g.x / (1.0f + __expf(-g.x)) * u.x, g.y / (1.0f + __expf(-g.y)) * u.y);
+      packed[word] = pack(__fdividef(g.x, 1.0f + __expf(-g.x)) * u.x, __fdividef(g.y, 1.0f + __expf(-g.y)) * u.y);
     }
     output[item] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
   }

@@ -82,8 +82,9 @@ __device__ __forceinline__ uint4 swiglu8(const uint4& gate, const uint4& up) {
     const float g_high = __uint_as_float(gates[word] & 0xffff0000u);
     const float u_low = __uint_as_float(ups[word] << 16);
     const float u_high = __uint_as_float(ups[word] & 0xffff0000u);
-    const __nv_bfloat162 two = __floats2bfloat162_rn(g_low / (1.0f + __expf(-g_low)) * u_low,
-                                                     g_high / (1.0f + __expf(-g_high)) * u_high);
+    const __nv_bfloat162 two = __floats2bfloat162_rn(
+        __fdividef(g_low, 1.0f + __expf(-g_low)) * u_low,
+        __fdividef(g_high, 1.0f + __expf(-g_high)) * u_high);
     packed[word] = *reinterpret_cast<const uint32_t*>(&two);
   }
   return make_uint4(packed[0], packed[1], packed[2], packed[3]);
@@ -124,7 +125,19 @@ nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__
   const uint32_t words[8] = {first.x, first.y, first.z, first.w,
                              second.x, second.y, second.z, second.w};
   uint32_t out[2] = {0u, 0u};
-  if (scale_code != 0u) {
+  // One correctly rounded reciprocal per block, then exact-rounded products: 16 divisions
+  // fewer per block (they made this memory-bound kernel arithmetic-bound). Where the
+  // reciprocal overflows (tensors whose largest magnitude is below about 1e-30) the block
+  // divides instead, as the written definition says.
+  const float inverse = __frcp_rn(denominator);
+  if (scale_code != 0u && inverse <= 3.402823466e38f) {
+#pragma unroll
+    for (int word = 0; word < 8; ++word) {
+      const float low = __fmul_rn(__uint_as_float(words[word] << 16), inverse);
+      const float high = __fmul_rn(__uint_as_float(words[word] & 0xffff0000u), inverse);
+      out[word / 4] |= encode_e2m1_pair(low, high) << ((word % 4) * 8);
+    }
+  } else if (scale_code != 0u) {
 #pragma unroll
     for (int word = 0; word < 8; ++word) {
       const float low = __fdiv_rn(__uint_as_float(words[word] << 16), denominator);

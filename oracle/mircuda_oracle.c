@@ -466,8 +466,9 @@ ORACLE_API uint8_t oracle_encode_e2m1(float value) {
  * tests/cutlass/fp4/mod.rs:21-24): parity unpinned; this function is the written spec.
  *   global = amax_tensor / (448 * 6)            (1.0 when the tensor is all zero)
  *   s_blk  = rne_ue4m3(amax_blk / (6 * global)) (one per 16 columns, swizzled layout)
- *   code   = rne_e2m1(x / (ue4m3(s_blk) * global)), saturating at +-6; 0 when s_blk is 0
- * All divisions are fp32. Returns the global scale through *global_scale.
+ *   code   = rne_e2m1(x * r), r = 1 / (ue4m3(s_blk) * global) rounded to fp32 once per block
+ *            (x / (ue4m3(s_blk) * global) where r overflows), saturating at +-6; 0 when s_blk is 0
+ * All divisions and products are fp32. Returns the global scale through *global_scale.
  */
 ORACLE_API void oracle_nvfp4_quantize_bf16(const uint16_t* input, uint8_t* codes, uint8_t* scales,
                                            float* global_scale, uint32_t rows, uint32_t k) {
@@ -489,11 +490,15 @@ ORACLE_API void oracle_nvfp4_quantize_bf16(const uint16_t* input, uint8_t* codes
       uint8_t scale_code = oracle_encode_ue4m3(block_max / (6.0f * global));
       scales[oracle_fp4_scale_index(row, block, k)] = scale_code;
       float denominator = oracle_ue4m3(scale_code) * global;
+      volatile float inverse = 1.0f / denominator;        /* rounded to fp32 here, once */
+      int by_product = inverse <= 3.402823466e38f;
       for (uint32_t item = 0; item < 16u; item += 2u) {
         uint8_t low = 0u, high = 0u;
         if (scale_code != 0u) {
-          low = oracle_encode_e2m1(oracle_bf16_to_float(values[item]) / denominator);
-          high = oracle_encode_e2m1(oracle_bf16_to_float(values[item + 1u]) / denominator);
+          float first = oracle_bf16_to_float(values[item]);
+          float second = oracle_bf16_to_float(values[item + 1u]);
+          low = oracle_encode_e2m1(by_product ? first * inverse : first / denominator);
+          high = oracle_encode_e2m1(by_product ? second * inverse : second / denominator);
         }
         codes[((size_t)row * k + (size_t)block * 16u + item) / 2u] = (uint8_t)(low | (high << 4));
       }
