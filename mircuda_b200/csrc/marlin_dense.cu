@@ -10,8 +10,9 @@
 // one thread's A fragment of mma.sync.m16n8k16 for a 16-row x 16-column weight block, so a
 // lane's 16-byte load covers four such blocks (64 output rows) of one 16-wide K tile, and its
 // eight scale bytes are 8 adjacent bytes. A CTA owns one 64-row tile of N and a K slice; its
-// eight warps take the slice's K tiles round-robin with all loads of a warp's share in flight
-// together, then add their accumulators through shared memory. K slices of one N tile meet in
+// eight warps take the slice's K tiles round-robin, each with a rolling window of four tiles'
+// loads in flight (weights, scales and its activation fragments straight from L1/L2; no barrier
+// in the loop), then add their accumulators through shared memory. K slices of one N tile meet in
 // the caller's `temporary` buffer; the slice that arrives last (a counter in the caller's
 // `locks`, which stay zero between launches) adds them in a fixed order. Nothing spins.
 #include <cuda_bf16.h>
@@ -31,7 +32,7 @@ constexpr int kWarps = 8;
 constexpr int kTileN = 64;
 constexpr int kTileK = 16;
 constexpr int kMaxTokens = 16;
-constexpr int kMaxTilesPerWarp = 8;        // K tiles whose loads one warp keeps in flight
+constexpr int kAhead = 4;                  // K tiles whose loads one warp keeps in flight
 
 using namespace marlin;
 
@@ -45,10 +46,7 @@ marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
                           int tiles_per_slice) {
   extern __shared__ __align__(16) uint8_t shared_raw[];
   constexpr int kRows = ROW_GROUPS * 8;
-  // Activations of the K slice: [kRows][slice_k + 8] bf16 (padded against bank conflicts).
-  __nv_bfloat16* shared_x = reinterpret_cast<__nv_bfloat16*>(shared_raw);
-  const int x_stride = kWarps * kMaxTilesPerWarp * kTileK + 8;   // one round of K-elements
-  float* shared_sums = reinterpret_cast<float*>(shared_raw);   // reused after the main loop
+  float* shared_sums = reinterpret_cast<float*>(shared_raw);   // the warps' sums meet here
   __shared__ bool last_arrival;
 
   const int tile_n = blockIdx.x;
@@ -72,82 +70,82 @@ marlin_nvfp4_dense_kernel(const __nv_bfloat16* __restrict__ input,
     }
   }
 
-  // The slice is walked in rounds of up to 64 K tiles (8 per warp, 1024 K-elements).
-  constexpr int kRoundTiles = kWarps * kMaxTilesPerWarp;
-  for (int round_tile = 0; round_tile < tiles_here; round_tile += kRoundTiles) {
-    const int round_tiles = min(kRoundTiles, tiles_here - round_tile);
-    // This warp's K tiles of the round: warp, warp + 8, ... All their loads go out first.
-    uint4 words[kMaxTilesPerWarp];
-    uint2 scale_bytes[kMaxTilesPerWarp];
+  // This warp's K tiles of the slice: warp, warp + 8, ... Nothing in the loop is shared between
+  // warps (activations come straight from L1/L2: the slice of x is at most 64 KB and every warp
+  // and CTA of the SM reads it), so there is no barrier and each warp keeps a rolling window of
+  // kAhead tiles' loads in flight: the loads for tile i + kAhead go out before tile i is used.
+  const int my_tiles = tiles_here > warp ? (tiles_here - warp + kWarps - 1) / kWarps : 0;
+  const uint4* weight_lane = weight + (static_cast<size_t>(first_tile_k + warp) * tiles_n + tile_n) * 32 + lane;
+  const uint8_t* scale_lane = scales + static_cast<size_t>(first_tile_k + warp) * n + tile_n * kTileN + group * 8;
+  const size_t weight_step = static_cast<size_t>(kWarps) * tiles_n * 32;      // uint4 per K-tile step
+  const size_t scale_step = static_cast<size_t>(kWarps) * n;
+  const __nv_bfloat16* x_lane = input + static_cast<size_t>(group) * k + (first_tile_k + warp) * kTileK + quad * 2;
+  bool row_valid[ROW_GROUPS];
 #pragma unroll
-    for (int item = 0; item < kMaxTilesPerWarp; ++item) {
-      const int local_tile = warp + item * kWarps;
-      words[item] = make_uint4(0u, 0u, 0u, 0u);
-      scale_bytes[item] = make_uint2(0u, 0u);
-      if (local_tile < round_tiles) {
-        const int tile_k = first_tile_k + round_tile + local_tile;
-        words[item] = load_streaming_16(weight + (static_cast<size_t>(tile_k) * tiles_n + tile_n) * 32 + lane);
-        scale_bytes[item] = __ldg(reinterpret_cast<const uint2*>(
-            scales + (static_cast<size_t>(tile_k) * n + tile_n * kTileN) + group * 8));
+  for (int rows = 0; rows < ROW_GROUPS; ++rows) row_valid[rows] = rows * 8 + group < tokens;
+
+  uint4 words[kAhead];
+  uint2 scale_bytes[kAhead];
+  uint32_t x_low[kAhead][ROW_GROUPS], x_high[kAhead][ROW_GROUPS];
+  auto fetch = [&](int slot, int item) {
+    words[slot] = make_uint4(0u, 0u, 0u, 0u);
+    scale_bytes[slot] = make_uint2(0u, 0u);
+#pragma unroll
+    for (int rows = 0; rows < ROW_GROUPS; ++rows) x_low[slot][rows] = x_high[slot][rows] = 0u;
+    if (item < my_tiles) {
+      words[slot] = load_streaming_16(weight_lane + item * weight_step);
+      scale_bytes[slot] = __ldg(reinterpret_cast<const uint2*>(scale_lane + item * scale_step));
+#pragma unroll
+      for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+        if (row_valid[rows]) {
+          const __nv_bfloat16* x = x_lane + static_cast<size_t>(rows) * 8 * k + item * (kWarps * kTileK);
+          x_low[slot][rows] = __ldg(reinterpret_cast<const uint32_t*>(x));
+          x_high[slot][rows] = __ldg(reinterpret_cast<const uint32_t*>(x + 8));
+        }
       }
     }
-
-    __syncthreads();   // the previous round's activations are no longer needed
-    // Activations of the round: 16-byte pieces (a K tile is two of them; k % 16 == 0 keeps
-    // every piece aligned in global memory, the row stride of shared_x is a multiple of 8).
-    const int round_pieces = round_tiles * 2;
-    for (int index = threadIdx.x; index < kRows * round_pieces; index += kThreads) {
-      const int row = index / round_pieces;
-      const int piece = index - row * round_pieces;
-      uint4 value = make_uint4(0u, 0u, 0u, 0u);
-      if (row < tokens) {
-        value = __ldg(reinterpret_cast<const uint4*>(
-                          input + static_cast<size_t>(row) * k + (first_tile_k + round_tile) * kTileK) + piece);
-      }
-      *reinterpret_cast<uint4*>(shared_x + row * x_stride + piece * 8) = value;
-    }
-    __syncthreads();
-
+  };
 #pragma unroll
-    for (int item = 0; item < kMaxTilesPerWarp; ++item) {
-      const int local_tile = warp + item * kWarps;
-      if (local_tile < round_tiles) {
-        // B fragments: activations of this K tile, token `group` of each row group.
-        uint32_t b[ROW_GROUPS][2];
+  for (int slot = 0; slot < kAhead; ++slot) fetch(slot, slot);
+
+  for (int base = 0; base < my_tiles; base += kAhead) {
+#pragma unroll
+    for (int slot = 0; slot < kAhead; ++slot) {
+      const uint4 word = words[slot];
+      const uint2 scale = scale_bytes[slot];
+      uint32_t b[ROW_GROUPS][2];
+#pragma unroll
+      for (int rows = 0; rows < ROW_GROUPS; ++rows) {
+        b[rows][0] = x_low[slot][rows];
+        b[rows][1] = x_high[slot][rows];
+      }
+      fetch(slot, base + slot + kAhead);
+      // A tile past the end carries zero words and zero scale codes: it adds nothing.
+      const uint32_t quarter_words[4] = {word.x, word.y, word.z, word.w};
+      // Scale bytes of rows (g, g+8) for quarters 0..3 sit at byte offsets 0,2 | 1,3 | 4,6 | 5,7.
+      const uint32_t low = scale.x;
+      const uint32_t high = scale.y;
+      const uint32_t code[4][2] = {{low & 0xffu, (low >> 16) & 0xffu},
+                                   {(low >> 8) & 0xffu, low >> 24},
+                                   {high & 0xffu, (high >> 16) & 0xffu},
+                                   {(high >> 8) & 0xffu, high >> 24}};
+#pragma unroll
+      for (int quarter = 0; quarter < 4; ++quarter) {
+        uint32_t a[4];
+        place_e2m1x8(quarter_words[quarter], a);   // (a0,a1) (a4,a5) (a2,a3) (a6,a7)
+        const uint32_t upper = scale_multiplier(code[quarter][0]);   // row g
+        const uint32_t lower = scale_multiplier(code[quarter][1]);   // row g + 8
+        const uint32_t a0 = mul_bf16x2(a[0], upper);
+        const uint32_t a1 = mul_bf16x2(a[2], lower);
+        const uint32_t a2 = mul_bf16x2(a[1], upper);
+        const uint32_t a3 = mul_bf16x2(a[3], lower);
 #pragma unroll
         for (int rows = 0; rows < ROW_GROUPS; ++rows) {
-          const __nv_bfloat16* x =
-              shared_x + (rows * 8 + group) * x_stride + local_tile * kTileK + quad * 2;
-          b[rows][0] = *reinterpret_cast<const uint32_t*>(x);
-          b[rows][1] = *reinterpret_cast<const uint32_t*>(x + 8);
-        }
-        const uint32_t quarter_words[4] = {words[item].x, words[item].y, words[item].z, words[item].w};
-        // Scale bytes of rows (g, g+8) for quarters 0..3 sit at byte offsets 0,2 | 1,3 | 4,6 | 5,7.
-        const uint32_t low = scale_bytes[item].x;
-        const uint32_t high = scale_bytes[item].y;
-        const uint32_t code[4][2] = {{low & 0xffu, (low >> 16) & 0xffu},
-                                     {(low >> 8) & 0xffu, low >> 24},
-                                     {high & 0xffu, (high >> 16) & 0xffu},
-                                     {(high >> 8) & 0xffu, high >> 24}};
-#pragma unroll
-        for (int quarter = 0; quarter < 4; ++quarter) {
-          uint32_t a[4];
-          place_e2m1x8(quarter_words[quarter], a);   // (a0,a1) (a4,a5) (a2,a3) (a6,a7)
-          const uint32_t upper = scale_multiplier(code[quarter][0]);   // row g
-          const uint32_t lower = scale_multiplier(code[quarter][1]);   // row g + 8
-          const uint32_t a0 = mul_bf16x2(a[0], upper);
-          const uint32_t a1 = mul_bf16x2(a[2], lower);
-          const uint32_t a2 = mul_bf16x2(a[1], upper);
-          const uint32_t a3 = mul_bf16x2(a[3], lower);
-#pragma unroll
-          for (int rows = 0; rows < ROW_GROUPS; ++rows) {
-            mma_bf16_16x8x16(accumulator[quarter][rows], a0, a1, a2, a3, b[rows][0], b[rows][1]);
-          }
+          mma_bf16_16x8x16(accumulator[quarter][rows], a0, a1, a2, a3, b[rows][0], b[rows][1]);
         }
       }
     }
   }
-  __syncthreads();   // everyone is done with shared_x; reuse the space for the warp sums
 
   // shared_sums[warp][n_local 0..63][row 0..kRows-1]
 #pragma unroll
@@ -248,9 +246,7 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
   slices = (tiles_k + tiles_per_slice - 1) / tiles_per_slice;
   const dim3 grid(tiles_n, slices);
   const int rows = tokens <= 8 ? 8 : 16;
-  const size_t x_bytes = static_cast<size_t>(rows) * (kWarps * kMaxTilesPerWarp * kTileK + 8) * 2;
-  const size_t sum_bytes = static_cast<size_t>(kWarps) * kTileN * rows * sizeof(float);
-  const size_t shared_bytes = x_bytes > sum_bytes ? x_bytes : sum_bytes;
+  const size_t shared_bytes = static_cast<size_t>(kWarps) * kTileN * rows * sizeof(float);
   auto cuda_stream = static_cast<cudaStream_t>(stream);
   if (tokens <= 8) {
     marlin_nvfp4_dense_kernel<1><<<grid, kThreads, shared_bytes, cuda_stream>>>(
