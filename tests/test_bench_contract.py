@@ -1,0 +1,61 @@
+"""bench.py prints one JSON line with the keys its callers read: the reference arm (CPU, runs
+everywhere) and the CUDA arm (GPU)."""
+import json
+import pathlib
+import subprocess
+import sys
+
+import pytest
+
+ROOT = pathlib.Path(__file__).resolve().parent.parent
+COMMON = ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better",
+          "scaling", "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e")
+
+
+def run_bench(*arguments, timeout):
+    completed = subprocess.run([sys.executable, str(ROOT / "bench.py"), *arguments], cwd=ROOT,
+                               capture_output=True, text=True, timeout=timeout)
+    assert completed.returncode == 0, completed.stderr[-2000:]
+    lines = [line for line in completed.stdout.splitlines() if line.startswith("{")]
+    assert len(lines) == 1, completed.stdout[-2000:]
+    return json.loads(lines[0])
+
+
+def check_common(record, steps, warmup):
+    for key in COMMON:
+        assert key in record, key
+    assert record["metric"] == "mxfp8_prefill_gemm_tflops" and record["unit"] == "TFLOP/s"
+    assert record["steps"] == steps and record["warmup"] == warmup and record["n_gpus"] == 1
+    assert record["higher_is_better"] is True and record["vs_baseline"] is None
+    assert record["value"] > 0 and record["ms_per_step"] > 0
+    assert "workload" in record["config"] and "model" not in record["config"]
+    baseline = record["cpu_baseline"]
+    assert baseline["kind"] in ("port", "reference") and baseline["cores"] >= 1 and baseline["sample"]
+    for key in ("value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"):
+        assert key in record["e2e"], key
+
+
+def test_reference_arm_line():
+    record = run_bench("--impl", "reference", "--steps", "1", "--warmup", "0", timeout=600)
+    check_common(record, 1, 0)
+    assert record["impl"] == "reference"
+    assert record["cpu_baseline"]["value"] == record["value"]
+    assert record["e2e"]["value"] == record["value"]
+    assert record["e2e"]["h2d_bytes_per_step"] == 0 and record["e2e"]["d2h_bytes_per_step"] == 0
+
+
+@pytest.mark.gpu
+def test_cuda_arm_line():
+    record = run_bench("--steps", "3", "--warmup", "3", timeout=600)
+    check_common(record, 3, 3)
+    assert "impl" not in record or record["impl"] != "reference"
+    roofline = record["roofline"]
+    for key in ("bound", "achieved", "peak", "unit", "frac", "traffic"):
+        assert key in roofline, key
+    assert roofline["bound"] == "tensor" and 0.0 < roofline["frac"] < 1.5
+    assert abs(roofline["frac"] - roofline["achieved"] / roofline["peak"]) < 1e-6
+    assert record["gpu_launches"] > 0
+    assert record["e2e"]["h2d_bytes_per_step"] > 0 and record["e2e"]["d2h_bytes_per_step"] > 0
+    assert record["e2e"]["value"] < record["value"]          # host copies are inside its timed region
+    for key in ("sm_mhz", "sm_max_mhz", "reasons"):
+        assert key in record["clocks"], key
