@@ -121,6 +121,14 @@ def test_fp4_vector_random(cuda_stream, fp4_vector_kernel, n, k):
 
 # ------------------------------------------------------------------ bf16 x NVFP4 skinny GEMM
 
+@pytest.fixture(params=["ring", "direct"])
+def nvfp4_vector_kernel(request, monkeypatch):
+    """Both kernels behind mircuda_b200_nvfp4_vector_*: weights through a TMA-fed shared-memory
+    ring, or loaded straight from global memory; the choice is read when a plan is created."""
+    monkeypatch.setenv("MIRCUDA_B200_NVFP4_VECTOR", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("m,n,k", [
     (m, n, k) for n, k in [(4096, 4096), (200, 448), (129, 64), (6144, 1024)] for m in [1, 4, 8, 3]
 ] + [
@@ -128,7 +136,7 @@ def test_fp4_vector_random(cuda_stream, fp4_vector_kernel, n, k):
     # units starts and ends inside tiles, and covers whole tiles in between.
     (8, 24576, 4096), (1, 24576, 4096), (8, 4096, 12288), (2, 12160, 2112),
 ])
-def test_nvfp4_vector_random(cuda_stream, m, n, k):
+def test_nvfp4_vector_random(cuda_stream, nvfp4_vector_kernel, m, n, k):
     from mircuda_b200 import plans
     w, ws = random_fp4(n, k, 21)
     x = seeded_bf16((m, k), 1.0, 3000 + m)
@@ -145,7 +153,7 @@ def test_nvfp4_vector_random(cuda_stream, m, n, k):
     assert_close_bf16(bf16_bits(out).reshape(m, n), expected, f"nvfp4 vector m={m} {n}x{k}")
 
 
-def test_nvfp4_vector_nibble_order(cuda_stream):
+def test_nvfp4_vector_nibble_order(cuda_stream, nvfp4_vector_kernel):
     """Asymmetric pattern: only even-k codes are non-zero, activations differ per k."""
     from mircuda_b200 import plans
     n, k = 128, 64
