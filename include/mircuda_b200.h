@@ -30,6 +30,12 @@ extern "C" {
 /* Library identification: (major << 16) | (minor << 8) | patch. NEW. */
 uint32_t mircuda_b200_version(void);
 
+/* Replaces `mircuda_cutlass_version` (sys/native/cutlass_probe.cu:16; declared in
+ * sys/src/lib.rs:33-44), which the crate's `cutlass` feature links unconditionally. No
+ * CUTLASS is linked here: the value is the release the reference pins
+ * (sys/build/sources.rs:8, v4.4.2 -> 40402), i.e. the plans this library stands in for. */
+unsigned int mircuda_cutlass_version(void);
+
 /* ------------------------------------------------------------------ MXFP8 quantizer ----
  * bf16 [rows, columns] -> E4M3 codes [rows, columns] + one E8M0 scale per 32 columns,
  * written straight into the 128x4-swizzled scale layout (`scales` must be zero-filled
@@ -57,6 +63,13 @@ size_t mircuda_mxfp8_tc_workspace_bytes(const void* plan);
 int mircuda_mxfp8_tc_execute(void* plan, void* stream, const void* a, const void* a_scales,
                              const void* b, const void* b_scales, void* c);
 void mircuda_mxfp8_tc_destroy(void* plan);
+
+/* NEW (diagnostic): proves the failure path of the bounded waits without disturbing the GPU.
+ * Enqueues a one-warp kernel that waits 2 ms on a barrier nothing arrives at; the wait runs
+ * out, the kernel returns by itself and raises the plan's status word exactly as a GEMM
+ * kernel whose wait ran out would, so every later `execute` of this plan returns -3. The
+ * plan is unusable afterwards (destroy it). */
+int mircuda_b200_mxfp8_tc_wait_probe(void* plan, void* stream);
 
 /* The same GEMM fused with the all-gather of a column-sharded linear. NEW (the reference is
  * single-GPU). The plan's n is this GPU's shard width; instead of a local C the epilogue

@@ -20,12 +20,14 @@ _vpp = ctypes.POINTER(ctypes.c_void_p)
 # name -> (restype, argtypes); mirrors include/mircuda_b200.h one to one.
 SIGNATURES = {
     "mircuda_b200_version": (_u32, []),
+    "mircuda_cutlass_version": (_u32, []),
     "mircuda_b200_mxfp8_quantize_bf16": (_i, [_vp, _vp, _vp, _u32, _u32, _vp]),
     "mircuda_b200_mxfp8_swizzle_scales": (_i, [_vp, _vp, _u32, _u32, _vp]),
     "mircuda_mxfp8_tc_create": (_i, [_i, _i, _i, _vp, _vpp]),
     "mircuda_mxfp8_tc_workspace_bytes": (_sz, [_vp]),
     "mircuda_mxfp8_tc_execute": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp]),
     "mircuda_mxfp8_tc_destroy": (None, [_vp]),
+    "mircuda_b200_mxfp8_tc_wait_probe": (_i, [_vp, _vp]),
     "mircuda_b200_mxfp8_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mircuda_fp4_create": (_i, [_i, _i, _i, _vp, _vpp]),
     "mircuda_fp4_workspace_bytes": (_sz, [_vp]),

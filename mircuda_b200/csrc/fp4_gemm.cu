@@ -103,6 +103,8 @@ extern "C" int mircuda_fp4_execute(void* raw, void* stream, const void* a, const
         reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u) != 0u) {
     return -1;
   }
+  // With n a multiple of 8 the epilogue writes 16-byte vectors: the output must allow them.
+  if (plan->n % 8 == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) != 0u) return -1;
   pair_gemm::Problem problem{static_cast<uint32_t>(plan->m), static_cast<uint32_t>(plan->n),
                              static_cast<uint32_t>(plan->k), plan->device, plan->sm_count,
                              plan->stream, plan->status};

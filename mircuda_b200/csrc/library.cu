@@ -1,4 +1,11 @@
 // Library identification.
 #include <cstdint>
 
-extern "C" uint32_t mircuda_b200_version(void) { return (0u << 16) | (1u << 8) | 0u; }
+extern "C" uint32_t mircuda_b200_version(void) { return (0u << 16) | (2u << 8) | 0u; }
+
+// The reference crate's `cutlass` feature links a no-argument symbol that reports the pinned
+// CUTLASS release as major * 10000 + minor * 100 + patch (sys/native/cutlass_probe.cu:16,
+// declared in sys/src/lib.rs:33-44, pin v4.4.2 in sys/build/sources.rs:8). This library links
+// no CUTLASS; it reports the release whose plans it stands in for so that the crate links
+// and callers comparing the number keep working.
+extern "C" unsigned int mircuda_cutlass_version(void) { return 4u * 10000u + 4u * 100u + 2u; }

@@ -463,6 +463,8 @@ extern "C" int mircuda_mxfp8_tc_execute(void* raw, void* stream, const void* a,
         reinterpret_cast<uintptr_t>(a_scales) | reinterpret_cast<uintptr_t>(b_scales)) & 15u) != 0u) {
     return -1;
   }
+  // With n a multiple of 8 the epilogue writes 16-byte vectors: the output must allow them.
+  if (plan->n % 8 == 0 && (reinterpret_cast<uintptr_t>(c) & 15u) != 0u) return -1;
   if (plan->pair) return execute_pair(plan, a, a_scales, b, b_scales, c);
   if (a != plan->cached_a) {
     const int status = encode_k_major_map(&plan->map_a, a, plan->m, plan->k, 1u, kBlockM);
@@ -515,6 +517,40 @@ extern "C" int mircuda_b200_mxfp8_tc_execute_gather(void* raw, void* stream, con
   gather.row_stride = static_cast<uint32_t>(row_stride);
   gather.column_offset = static_cast<uint32_t>(column_offset);
   return execute_pair(plan, a, a_scales, b, b_scales, outputs[0], gather);
+}
+
+namespace mircuda_b200 {
+namespace mxfp8_gemm {
+
+// One warp waits, with a 2 ms budget instead of the kernels' half second, on a barrier that
+// nothing ever arrives at, and leaves the way the GEMM roles leave when a wait runs out: the
+// wait raises the CTA's abort flag and returns false, and thread 0 reports it through the
+// plan's status word. The kernel always returns by itself.
+__global__ void __launch_bounds__(32) wait_probe_kernel(uint32_t* __restrict__ status) {
+  __shared__ uint64_t barrier;
+  __shared__ uint32_t abort_flag;
+  volatile uint32_t* abort = &abort_flag;
+  if (threadIdx.x == 0) {
+    ptx::mbarrier_init(&barrier, 1);
+    *abort = 0u;
+    ptx::fence_barrier_init();
+  }
+  __syncwarp();
+  ptx::mbarrier_wait<2ull * 1000ull * 1000ull>(&barrier, 0u, abort);
+  __syncwarp();
+  if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
+}
+
+}  // namespace mxfp8_gemm
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_mxfp8_tc_wait_probe(void* raw, void* stream) {
+  using namespace mircuda_b200::mxfp8_gemm;
+  if (raw == nullptr || stream == nullptr) return -1;
+  auto* plan = static_cast<Plan*>(raw);
+  if (static_cast<cudaStream_t>(stream) != plan->stream) return -1;
+  wait_probe_kernel<<<1, 32, 0, plan->stream>>>(plan->status);
+  return static_cast<int>(cudaPeekAtLastError());
 }
 
 extern "C" void mircuda_mxfp8_tc_destroy(void* raw) {

@@ -88,6 +88,7 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // orders of magnitude beyond any legitimate wait in these kernels.
 constexpr uint64_t kWaitBudgetNs = 500ull * 1000ull * 1000ull;
 
+template <uint64_t BUDGET_NS = kWaitBudgetNs>
 __device__ __forceinline__ bool mbarrier_wait(uint64_t* barrier, uint32_t parity,
                                               volatile uint32_t* abort) {
   if (mbarrier_try_wait(barrier, parity)) return true;
@@ -96,7 +97,7 @@ __device__ __forceinline__ bool mbarrier_wait(uint64_t* barrier, uint32_t parity
     if (mbarrier_try_wait(barrier, parity)) return true;
     if ((poll & 15u) == 0u) {
       if (*abort != 0u) return false;
-      if (global_timer_ns() - start > kWaitBudgetNs) break;
+      if (global_timer_ns() - start > BUDGET_NS) break;
     }
   }
   *abort = 1u;

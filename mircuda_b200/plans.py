@@ -35,6 +35,11 @@ class StreamMismatch(RuntimeError):
     pass
 
 
+class MisalignedOperand(ValueError):
+    """An operand's address does not allow the 16-byte accesses the kernel makes (the C ABI
+    answers -1 for it; the host mirror names the operand instead)."""
+
+
 class NativeError(RuntimeError):
     def __init__(self, status: int):
         super().__init__(f"native call failed with status {status}")
@@ -49,6 +54,13 @@ def _check(status: int) -> None:
 def _exact(operand: str, expected: int, tensor: torch.Tensor) -> None:
     if tensor.numel() != expected:
         raise MatmulLengthMismatch(operand, expected, tensor.numel())
+
+
+def _require_vector_output(operand: str, n: int, tensor: torch.Tensor) -> None:
+    """With n a multiple of 8 the GEMM epilogues store 16-byte vectors, so the output must
+    start on a 16-byte boundary (a sub-buffer of a pool might not)."""
+    if n % 8 == 0 and tensor.data_ptr() % 16 != 0:
+        raise MisalignedOperand(f"{operand} must be 16-byte aligned when n % 8 == 0")
 
 
 def _device_pointer(tensor: torch.Tensor, dtypes) -> ctypes.c_void_p:
@@ -121,6 +133,7 @@ class BlockScaledMxFp8Plan:
             _exact("B", s.n * s.k, b)
         _exact("B scales", s.scale_bytes(s.n), b_scales)
         _exact("C", s.m * s.n, output)
+        _require_vector_output("C", s.n, output)
         _check(self._lib.mircuda_mxfp8_tc_execute(
             self._raw, _stream_handle(stream), _device_pointer(a, _BYTES),
             _device_pointer(a_scales, _BYTES), _device_pointer(b, _WORDS),

@@ -8,7 +8,7 @@ import torch
 
 from . import _lib
 from .plans import (InvalidMatmulShape, StreamMismatch, _BF16, _BYTES, _check, _device_pointer,
-                    _exact, _stream_handle)
+                    _exact, _require_vector_output, _stream_handle)
 
 
 @dataclass(frozen=True)
@@ -50,6 +50,7 @@ class BlockScaledFp4Plan:
         _exact("B", s.n * s.k // 2, b)
         _exact("B scales", s.scale_bytes(s.n), b_scales)
         _exact("C", s.m * s.n, output)
+        _require_vector_output("C", s.n, output)
         _check(self._lib.mircuda_fp4_execute(
             self._raw, _stream_handle(stream), _device_pointer(a, _BYTES),
             _device_pointer(a_scales, _BYTES), _device_pointer(b, _BYTES),

@@ -276,12 +276,19 @@ def nvfp4_dequantize(codes: np.ndarray, scales: np.ndarray, k: int) -> np.ndarra
     return (values.reshape(rows, k // 16, 16) * decoded_scales[:, :, None]).reshape(rows, k)
 
 
-def nvfp4_quantize(values_bf16: np.ndarray) -> tuple[np.ndarray, np.ndarray, float]:
-    """bf16 bits [rows, K] -> (packed codes, swizzled UE4M3 scales, global). Parity unpinned."""
+def nvfp4_quantize(values_bf16: np.ndarray, global_scale: float | None = None
+                   ) -> tuple[np.ndarray, np.ndarray, float]:
+    """bf16 bits [rows, K] -> (packed codes, swizzled UE4M3 scales, global). Parity unpinned.
+    With `global_scale` given, the tensor scale is that value instead of amax / (448 * 6)."""
     values = _c(values_bf16, np.uint16)
     rows, k = values.shape
     codes = np.zeros((rows, k // 2), dtype=np.uint8)
     scales = np.zeros(fp4_scale_bytes(rows, k), dtype=np.uint8)
+    if global_scale is not None:
+        lib().oracle_nvfp4_quantize_bf16_scaled(_ptr(values, _u16p), _ptr(codes, _u8p),
+                                                _ptr(scales, _u8p), ctypes.c_float(global_scale),
+                                                ctypes.c_uint32(rows), ctypes.c_uint32(k))
+        return codes, scales, float(np.float32(global_scale))
     global_scale = ctypes.c_float(0.0)
     lib().oracle_nvfp4_quantize_bf16(_ptr(values, _u16p), _ptr(codes, _u8p), _ptr(scales, _u8p),
                                      ctypes.byref(global_scale), ctypes.c_uint32(rows),
@@ -314,6 +321,45 @@ def nvfp4_gemv_bf16(x_bf16, w_codes, w_scales, n: int, k: int, global_scale: flo
     weights = nvfp4_dequantize(np.asarray(w_codes).reshape(n, k // 2), w_scales, k)
     product = (bf16_to_f32(x) @ weights.T) * np.float32(global_scale)
     return f32_to_bf16(product.astype(np.float32))
+
+
+# ------------------------------------------------------------------ int4-g128 W4A16
+# No reference entry point executes this format; the numerics restated here are the ones the
+# reference's (unused) int4 dequantiser defines, sys/native/marlin/vendor/dequant.h:107-216:
+# unsigned 4-bit codes with the symmetric zero point 8 folded in, weight = (q - 8) * scale, f16
+# group scales, one per 128 K-elements. Parity unpinned: no reference test or kernel runs it.
+
+INT4_GROUP = 128
+
+
+def int4_g128_quantize(weights_f32: np.ndarray) -> tuple[np.ndarray, np.ndarray]:
+    """fp32 [n, k] -> (packed codes u8 [n, k/2], even k in the low nibble; f16 scales [n, k/128]),
+    scale = max|w| / 7 per group rounded to f16, code = clamp(rne(w / scale) + 8, 0, 15)."""
+    weights = np.asarray(weights_f32, dtype=np.float32)
+    n, k = weights.shape
+    groups = weights.reshape(n, k // INT4_GROUP, INT4_GROUP)
+    scales = (np.max(np.abs(groups), axis=-1) / np.float32(7.0)).astype(np.float16)
+    safe = np.where(scales == 0, np.float16(1.0), scales).astype(np.float32)
+    codes = np.clip(np.rint(groups / safe[..., None]) + 8, 0, 15).astype(np.uint8).reshape(n, k)
+    packed = np.ascontiguousarray(codes[:, 0::2] | (codes[:, 1::2] << 4))
+    return packed, np.ascontiguousarray(scales)
+
+
+def int4_g128_dequantize(packed: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:
+    """(q - 8) * scale as fp32 [n, k]; exact (a 4-bit integer times an f16 fits fp32)."""
+    packed = _c(packed, np.uint8)
+    n = packed.shape[0]
+    codes = np.empty((n, packed.shape[1] * 2), dtype=np.float32)
+    codes[:, 0::2] = packed & 0xF
+    codes[:, 1::2] = packed >> 4
+    scales = np.asarray(scales_f16, dtype=np.float16).astype(np.float32)
+    return ((codes - np.float32(8.0)).reshape(n, -1, INT4_GROUP) * scales[:, :, None]).reshape(n, -1)
+
+
+def w4a16_int4(x_f16: np.ndarray, packed: np.ndarray, scales_f16: np.ndarray) -> np.ndarray:
+    """f16 activations [m, k] x int4-g128 weights [n, k] -> f16 [m, n], fp32 accumulation."""
+    x = np.asarray(x_f16, dtype=np.float16).astype(np.float32)
+    return (x @ int4_g128_dequantize(packed, scales_f16).T).astype(np.float16)
 
 
 # ------------------------------------------------------------------ dense GEMV and grouped

@@ -7,7 +7,7 @@
  * suite, the smoke check and the benchmark's cpu_baseline / reference arm may use it.
  *
  * Parity pins: the codec and the quantizer are pinned bit-exactly against the
- * reference's own helper functions compiled for the host (oracle/build_ref.py) and
+ * reference's own helper functions compiled for the host (oracle/build.py) and
  * against the reference tests' golden vectors (tests/test_oracle_golden.py). The
  * NVFP4 quantizer has no counterpart in the reference: parity unpinned for it.
  *
@@ -470,6 +470,9 @@ ORACLE_API uint8_t oracle_encode_e2m1(float value) {
  *            (x / (ue4m3(s_blk) * global) where r overflows), saturating at +-6; 0 when s_blk is 0
  * All divisions and products are fp32. Returns the global scale through *global_scale.
  */
+static void nvfp4_quantize_rows(const uint16_t* input, uint8_t* codes, uint8_t* scales,
+                                float global, uint32_t rows, uint32_t k);
+
 ORACLE_API void oracle_nvfp4_quantize_bf16(const uint16_t* input, uint8_t* codes, uint8_t* scales,
                                            float* global_scale, uint32_t rows, uint32_t k) {
   float amax = 0.0f;
@@ -479,6 +482,19 @@ ORACLE_API void oracle_nvfp4_quantize_bf16(const uint16_t* input, uint8_t* codes
   }
   float global = amax > 0.0f ? amax / 2688.0f : 1.0f;
   *global_scale = global;
+  nvfp4_quantize_rows(input, codes, scales, global, rows, k);
+}
+
+/* The same block scales and codes for a global scale the caller fixed beforehand (a calibrated
+ * activation scale shared by several tensors): steps 2 and 3 of the spec above. */
+ORACLE_API void oracle_nvfp4_quantize_bf16_scaled(const uint16_t* input, uint8_t* codes,
+                                                  uint8_t* scales, float global_scale,
+                                                  uint32_t rows, uint32_t k) {
+  nvfp4_quantize_rows(input, codes, scales, global_scale, rows, k);
+}
+
+static void nvfp4_quantize_rows(const uint16_t* input, uint8_t* codes, uint8_t* scales,
+                                float global, uint32_t rows, uint32_t k) {
   for (uint32_t row = 0; row < rows; ++row) {
     for (uint32_t block = 0; block < k / 16u; ++block) {
       const uint16_t* values = input + (size_t)row * k + (size_t)block * 16u;

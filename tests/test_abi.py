@@ -31,7 +31,9 @@ def test_header_symbols_are_exported(library):
 
 
 def test_version(library):
-    assert library.mircuda_b200_version() == (1 << 8)
+    assert library.mircuda_b200_version() == (2 << 8)
+    # sys/native/cutlass_probe.cu:16 with the pin of sys/build/sources.rs:8 (v4.4.2)
+    assert library.mircuda_cutlass_version() == 40402
 
 
 def test_argument_validation_needs_no_gpu(library):

@@ -81,28 +81,59 @@ def test_dense_random(cuda_stream, dtype, m, n, k, alpha, beta):
     assert_close(c, expected, f"dense {dtype} {m}x{n}x{k}")
 
 
-def w4a16_reference(x, packed, scales):
-    codes = torch.stack([packed & 15, packed >> 4], dim=-1).reshape(packed.shape[0], -1).double()
-    weights = (codes - 8.0) * scales.double().repeat_interleave(128, dim=1)
-    return x.double() @ weights.T
+def run_w4a16(stream, x, packed, scales, m, n, k):
+    from mircuda_b200 import dense
+    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
+    plan = dense.W4A16Plan(stream, dense.W4A16Spec(m, n, k))
+    torch.cuda.synchronize()
+    for _ in range(2):
+        plan.execute(stream, x.view(-1), packed.view(-1), scales.view(-1), out.view(-1))
+    stream.synchronize()
+    plan.close()
+    return out
+
+
+def assert_w4a16_matches_oracle(out, x, packed, scales, what):
+    import oracle
+    expected = oracle.w4a16_int4(x.cpu().numpy(), packed.cpu().numpy(), scales.cpu().numpy())
+    assert_close(out, torch.from_numpy(expected.astype(np.float32)), what)
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (4, 1000, 512), (8, 200, 128), (16, 640, 2048),
                                    (9, 4096, 4096), (256, 512, 1024), (40, 264, 384)])
 def test_w4a16_random(cuda_stream, m, n, k):
+    """Device quantiser (bit-exact against the oracle's) and the product against the oracle's
+    (q - 8) * scale restatement, sys/native/marlin/vendor/dequant.h:107-216."""
+    import oracle
     from mircuda_b200 import dense
     generator = torch.Generator(device="cuda").manual_seed(8200 + m)
     weight = torch.randn(n, k, generator=generator, device="cuda") * 0.02
     packed, scales = dense.quantize_int4(weight)
+    oracle_packed, oracle_scales = oracle.int4_g128_quantize(weight.cpu().numpy())
+    assert np.array_equal(scales.cpu().numpy().view(np.uint16), oracle_scales.view(np.uint16))
+    assert np.array_equal(packed.cpu().numpy(), oracle_packed)
     x = torch.randn(m, k, generator=generator, device="cuda").to(torch.float16)
-    out = torch.full((m, n), float("nan"), dtype=torch.float16, device="cuda")
-    plan = dense.W4A16Plan(cuda_stream, dense.W4A16Spec(m, n, k))
-    torch.cuda.synchronize()
-    for _ in range(2):
-        plan.execute(cuda_stream, x.view(-1), packed.view(-1), scales.view(-1), out.view(-1))
-    cuda_stream.synchronize()
-    plan.close()
-    assert_close(out, w4a16_reference(x, packed, scales), f"w4a16 {m}x{n}x{k}")
+    out = run_w4a16(cuda_stream, x, packed, scales, m, n, k)
+    assert_w4a16_matches_oracle(out, x, packed, scales, f"w4a16 {m}x{n}x{k}")
+
+
+@pytest.mark.parametrize("m", [1, 16, 256])
+@pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
+def test_w4a16_benchmark_shapes(cuda_stream, m, n, k):
+    """The Marlin-style W4A16 shapes the throughput is quoted on: K=4096 x N=14336 and
+    K=14336 x N=4096, weights ~N(0, 0.02) quantised by the oracle (symmetric zero point 8,
+    group 128, f16 scales = max|w|/7), f16 activations ~N(0, 1) at M in {1, 16, 256}."""
+    import oracle
+    rng = np.random.default_rng(4000 + n // 64 + m)
+    weight = rng.standard_normal((n, k), dtype=np.float32) * np.float32(0.02)
+    packed_host, scales_host = oracle.int4_g128_quantize(weight)
+    x_host = rng.standard_normal((m, k), dtype=np.float32).astype(np.float16)
+    packed = torch.from_numpy(packed_host).cuda()
+    scales = torch.from_numpy(scales_host).cuda()
+    x = torch.from_numpy(x_host).cuda()
+    out = run_w4a16(cuda_stream, x, packed, scales, m, n, k)
+    expected = oracle.w4a16_int4(x_host, packed_host, scales_host)
+    assert_close(out, torch.from_numpy(expected.astype(np.float32)), f"w4a16 {m}x{n}x{k}")
 
 
 def test_w4a16_nibble_order(cuda_stream):

@@ -106,3 +106,17 @@ def test_scaled_fp8_spec_validation():
         dense.ScaledFp8Spec(1, 16, 16, torch.float16)
     with pytest.raises(plans.InvalidMatmulShape):
         dense.ScaledFp8Spec(1, 16, 16, torch.float32, "row")
+
+
+def test_output_alignment_rule_of_the_gemm_plans():
+    """The GEMM epilogues store 16-byte vectors when n % 8 == 0; an output that starts
+    elsewhere (a sub-buffer of a pool) is refused on the host, as the C ABI refuses it (-1)."""
+    from mircuda_b200 import plans
+    pool = torch.zeros(64, dtype=torch.bfloat16)
+    base = pool.data_ptr() % 16 // 2                 # elements past a 16-byte boundary
+    aligned = pool[(8 - base) % 8:][:16]
+    shifted = pool[(8 - base) % 8 + 1:][:16]
+    plans._require_vector_output("C", 8, aligned)
+    plans._require_vector_output("C", 12, shifted)   # scalar store path: no rule
+    with pytest.raises(plans.MisalignedOperand):
+        plans._require_vector_output("C", 8, shifted)

@@ -183,11 +183,16 @@ def test_gemm_rejects_other_stream_and_bad_lengths(cuda_stream):
     plan.close()
 
 
-def test_prefill_shape_rows_against_oracle(cuda_stream):
-    """Qwen3-8B O-projection shape (4096 x 4096 x 4096), device-quantized activations, checked
-    on a sample of output rows against the oracle (each output row depends on one A row)."""
+@pytest.mark.parametrize("name,n,k", [("qkv", 6144, 4096), ("o", 4096, 4096),
+                                      ("gate_up", 24576, 4096), ("down", 4096, 12288)])
+def test_prefill_shape_rows_against_oracle(cuda_stream, name, n, k):
+    """The four Qwen3-8B prefill linears at M = 4096 (the shapes the throughput is quoted on),
+    activations quantized on the device as src/mxfp8/tensor_core.rs:127-162 does, checked on
+    output rows taken from the first, a middle and the last 256-row tile against the oracle.
+    Whole rows are compared, so every column tile (first to last) of those rows is covered;
+    each output row depends on one A row only."""
     from mircuda_b200 import plans
-    m, n, k = 4096, 4096, 4096
+    m = 4096
     x = seeded_bf16((m, k), 1.0, 2000)
     w = seeded_bf16((n, k), 0.02, 2001)
     spec = plans.MxFp8Spec(m, k, n)
@@ -199,7 +204,7 @@ def test_prefill_shape_rows_against_oracle(cuda_stream):
     plans.mxfp8_quantize_bf16(cuda_stream, w, w_codes, w_scales)
     operation.execute(cuda_stream, x.view(-1), w_codes, w_scales, output)
     cuda_stream.synchronize()
-    rows = np.array([0, 1, 127, 128, 1000, 2047, 2048, 3333, 4095])
+    rows = np.array([0, 1, 127, 128, 255, 2047, 2048, 2177, 3840, 3967, 3968, 4095])
     a_codes, a_scales = oracle.mxfp8_quantize(bf16_bits(x)[rows])
     # quantization is per row block, so quantizing the sampled rows alone gives the same codes
     device_codes = operation.scratch.quantized_input.view(m, k)[torch.from_numpy(rows).cuda()].cpu().numpy()
@@ -207,4 +212,55 @@ def test_prefill_shape_rows_against_oracle(cuda_stream):
     b_dequantized = oracle.mxfp8_dequantize(w_codes.cpu().numpy().reshape(n, k), w_scales.cpu().numpy())
     expected = oracle.f32_to_bf16(oracle.mxfp8_dequantize(a_codes, a_scales) @ b_dequantized.T)
     actual = bf16_bits(output).reshape(m, n)[rows]
-    assert_close_bf16(actual, expected, "prefill O-projection rows")
+    assert_close_bf16(actual, expected, f"prefill {name} rows")
+
+
+def test_gemm_refuses_an_output_that_cannot_take_vector_stores(cuda_stream):
+    """n % 8 == 0 selects 16-byte stores in the epilogue: an output that is only 2-byte aligned
+    gets status -1 from the C ABI instead of a misaligned-address fault, and the host mirror
+    names the operand."""
+    from mircuda_b200 import plans
+    plan = plans.BlockScaledMxFp8Plan(cuda_stream, plans.BlockScaledMxFp8Spec(128, 128, 128))
+    codes = torch.zeros(128 * 128, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(512, dtype=torch.uint8, device="cuda")
+    pool = torch.zeros(128 * 128 + 8, dtype=torch.bfloat16, device="cuda")
+    shifted = pool[1:1 + 128 * 128]
+    with pytest.raises(plans.MisalignedOperand):
+        plan.execute(cuda_stream, codes, scales, codes, scales, shifted)
+    pointer = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    status = plan._lib.mircuda_mxfp8_tc_execute(
+        plan._raw, ctypes.c_void_p(cuda_stream.cuda_stream), pointer(codes), pointer(scales),
+        pointer(codes), pointer(scales), pointer(shifted))
+    assert status == -1
+    plan.close()
+
+
+def test_a_wait_that_runs_out_reports_minus_three(cuda_stream):
+    """Failure path of the bounded waits: a kernel waits (2 ms budget) on a barrier nothing
+    arrives at, gives up by itself and raises the plan's status word; the context stays usable,
+    the plan's next execute answers -3 and other plans keep working."""
+    import time
+    from mircuda_b200 import plans
+    plan = plans.BlockScaledMxFp8Plan(cuda_stream, plans.BlockScaledMxFp8Spec(128, 128, 128))
+    codes = torch.full((128 * 128,), 0x38, dtype=torch.uint8, device="cuda")
+    scales = torch.full((512,), 127, dtype=torch.uint8, device="cuda")
+    out = torch.zeros(128 * 128, dtype=torch.bfloat16, device="cuda")
+    torch.cuda.synchronize()
+    plan.execute(cuda_stream, codes, scales, codes, scales, out)      # healthy first
+    cuda_stream.synchronize()
+    assert (out.float() == 128.0).all()
+    begin = time.perf_counter()
+    assert plan._lib.mircuda_b200_mxfp8_tc_wait_probe(plan._raw, ctypes.c_void_p(cuda_stream.cuda_stream)) == 0
+    cuda_stream.synchronize()                                          # the kernel returned by itself
+    assert time.perf_counter() - begin < 5.0
+    with pytest.raises(plans.NativeError) as failure:
+        plan.execute(cuda_stream, codes, scales, codes, scales, out)
+    assert failure.value.status == -3
+    plan.close()
+    healthy = plans.BlockScaledMxFp8Plan(cuda_stream, plans.BlockScaledMxFp8Spec(128, 128, 128))
+    out.zero_()
+    torch.cuda.synchronize()
+    healthy.execute(cuda_stream, codes, scales, codes, scales, out)
+    cuda_stream.synchronize()
+    assert (out.float() == 128.0).all()
+    healthy.close()

@@ -245,3 +245,22 @@ def test_scaled_fp8_golden():
     assert (out.reshape(-1) == expected).all()
     out = oracle.scaled_fp8(ones_x, ones_w, [0.5], [0.25], None, 1, 16, 16)
     assert (oracle.bf16_to_f32(out) == 2.0).all()
+
+
+def test_int4_g128_known_answers():
+    """int4 with symmetric zero point 8 (sys/native/marlin/vendor/dequant.h:107-216: the
+    dequantiser subtracts 8, weight = (q - 8) * scale): a group whose largest magnitude is 7
+    gets scale 1 and codes value + 8, packed with the even k in the low nibble; the product is
+    the plain dot product of the dequantised weights."""
+    values = np.tile(np.arange(-7, 8, dtype=np.float32), 9)[:128]
+    weights = np.stack([values, -values * 0.5])
+    packed, scales = oracle.int4_g128_quantize(weights)
+    assert scales.dtype == np.float16 and scales.tolist() == [[1.0], [0.5]]
+    assert packed[0, 0] == ((-7 + 8) | ((-6 + 8) << 4)) and packed[0, 7] == (15 | (1 << 4))
+    assert np.array_equal(oracle.int4_g128_dequantize(packed, scales), weights)
+    x = np.arange(128, dtype=np.float32).astype(np.float16).reshape(1, 128) / 64
+    out = oracle.w4a16_int4(x, packed, scales)
+    expected = (x.astype(np.float32) @ weights.T).astype(np.float16)
+    assert np.array_equal(out, expected)
+    zero_packed, zero_scales = oracle.int4_g128_quantize(np.zeros((1, 128), np.float32))
+    assert zero_scales[0, 0] == 0 and (zero_packed == 0x88).all()

@@ -49,6 +49,33 @@ def test_dense_vector(cuda_stream, n, k, data_type):
         a = actual.view(np.float16).astype(np.float64)
         e = expected.view(np.float16).astype(np.float64)
         assert np.max(np.abs(a - e)) <= 1e-2 * np.max(np.abs(e))
+    path = oracle.ref_library("vector")
+    if path is not None:
+        # The reference's own kernel (sys/native/dense_vector_sm120.cu:147-175, compiled from
+        # its source for sm_100a), same inputs, through its own entry points.
+        library = ctypes.CDLL(str(path))
+        raw = ctypes.c_void_p()
+        stream = ctypes.c_void_p(cuda_stream.cuda_stream)
+        assert library.mircuda_dense_vector_create(data_type, n, k, stream, ctypes.byref(raw)) == 0
+        reference_y = expected_input.clone()
+        torch.cuda.synchronize()
+        library.mircuda_dense_vector_execute.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_float] * 2
+        assert library.mircuda_dense_vector_execute(
+            raw, stream, ctypes.c_void_p(x.data_ptr()), ctypes.c_void_p(w.data_ptr()),
+            ctypes.c_void_p(reference_y.data_ptr()), ctypes.c_float(1.5), ctypes.c_float(0.25)) == 0
+        cuda_stream.synchronize()
+        library.mircuda_dense_vector_destroy.argtypes = [ctypes.c_void_p]
+        library.mircuda_dense_vector_destroy(raw)
+        reference_bits = reference_y.view(view).cpu().numpy().view(np.uint16)
+        # pins the restatement (different summation order, so a tolerance) and this library
+        if data_type:
+            assert_close_bf16(expected, reference_bits, f"oracle vs reference dense kernel {n}x{k}")
+            assert_close_bf16(actual, reference_bits, f"dense bf16 vs reference kernel {n}x{k}")
+        else:
+            r = reference_bits.view(np.float16).astype(np.float64)
+            e = expected.view(np.float16).astype(np.float64)
+            assert np.max(np.abs(e - r)) <= 1e-2 * np.max(np.abs(r))
+            assert np.max(np.abs(a - r)) <= 1e-2 * np.max(np.abs(r))
     # beta = 0 must not read the output (NaN-prefilled, reference idiom tests/cutlass/grouped/bf16.rs:28)
     y2 = torch.full((n,), float("nan"), dtype=dtype, device="cuda")
     torch.cuda.synchronize()
