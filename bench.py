@@ -10,8 +10,14 @@ data: activations ~N(0,1), weights ~N(0,0.02), bf16, weights quantized once up f
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
 
 Prints one JSON line. ``value`` is device-resident throughput (GEMM flops of a step over
-the step time, quantizers included); ``e2e`` is the same through the public API with host
-buffers (pinned), H2D of every activation and D2H of every output inside the timed region.
+the step time, quantizers included). The ``--steps`` loop is timed as one region and repeated
+until about two seconds of timed work have run, so that the clocks settle under the power cap
+and dozens of clock samples land inside; ``ms_per_step`` is the median repeat (min and max are
+printed beside it). ``e2e`` is the same through the public API with host buffers (pinned), H2D
+of every activation and D2H of every output inside the timed region. At one GPU the line also
+carries ``decode`` (the bf16 x NVFP4 decode GEMV at the same four weight shapes, M in {1,4,8},
+HBM GB/s: the other half of the headline metric) and ``reference_kernels`` (the reference's own
+sm_100a-runnable kernels timed beside this library's for the same op).
 With N > 1 the weight N dimension is column-sharded across ranks and outputs are
 all-gathered (strong scaling). ``--impl reference`` times the CPU restatement of the
 reference's dequantize-then-matmul on the host cores (the reference has no CPU
@@ -21,16 +27,19 @@ from __future__ import annotations
 
 import argparse
 import json
+import math
 import os
 import statistics
-import subprocess
 import sys
-import threading
 import time
 from pathlib import Path
 
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
+
+NOMINAL_FP8_TFLOPS = 4500.0        # dense FP8 of one B200, vendor figure
+NVLINK_GBS_PER_DIRECTION = 900.0   # NVLink 5, per GPU and direction, vendor figure
+TIMED_REGION_SECONDS = 2.0         # the --steps loop is repeated until this much has been timed
 
 SHAPES = [  # name, N, K
     ("qkv", 6144, 4096),
@@ -53,63 +62,6 @@ def measured_peaks() -> dict:
     if path.exists():
         return json.loads(path.read_text())
     return {}
-
-
-class ClockSampler:
-    """Samples SM clocks and throttle reasons through NVML while the timed region runs
-    (read-only queries, one every few milliseconds; `nvidia-smi` would take ~100 ms a call)."""
-
-    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
-               0x4: "sw_power_cap"}
-
-    def __init__(self, index: int):
-        self.index = index
-        self.clocks: list[int] = []
-        self.maximum = None
-        self.reasons: set[str] = set()
-        self._stop = threading.Event()
-        self._thread = threading.Thread(target=self._run, daemon=True)
-
-    def _run(self):
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
-            index = self.index
-            if visible:
-                entry = visible.split(",")[self.index].strip()
-                index = int(entry) if entry.isdigit() else self.index
-            handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.maximum = int(pynvml.nvmlDeviceGetMaxClockInfo(handle, pynvml.NVML_CLOCK_SM))
-        except Exception:
-            return
-        while not self._stop.is_set():
-            try:
-                self.clocks.append(int(pynvml.nvmlDeviceGetClockInfo(handle, pynvml.NVML_CLOCK_SM)))
-                mask = int(pynvml.nvmlDeviceGetCurrentClocksEventReasons(handle))
-                for bit, name in self.REASONS.items():
-                    if mask & bit:
-                        self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(0.004)
-
-    def __enter__(self):
-        self._thread.start()
-        return self
-
-    def __exit__(self, *exc):
-        self._stop.set()
-        self._thread.join(timeout=10)
-
-    def summary(self) -> dict:
-        return {
-            "sm_mhz": statistics.median(self.clocks) if self.clocks else None,
-            "sm_min_mhz": min(self.clocks) if self.clocks else None,
-            "sm_max_mhz": self.maximum,
-            "reasons": sorted(self.reasons),
-            "samples": len(self.clocks),
-        }
 
 
 # ----------------------------------------------------------------------------- reference arm
@@ -191,6 +143,48 @@ def cpu_baseline_leg() -> dict:
 
 
 # ------------------------------------------------------------------------------- GPU arm
+
+def fp8_peak_probe(torch, stream) -> dict | None:
+    """Measured dense FP8 tensor peak of this GPU: cuBLASLt E4M3 x E4M3 -> bf16 at 8192^3 through
+    `torch._scaled_mm` with per-tensor scales (a library GEMM, used only as the roofline's
+    denominator, outside every timed region of the benchmark). `burst` is the best single call
+    after a pause, `sustained` the rate of a loop about two seconds long under the power cap.
+    Returns None when the call is not available."""
+    try:
+        size = 8192
+        with torch.cuda.stream(stream):
+            a = (torch.randn(size, size, device="cuda") * 0.5).to(torch.float8_e4m3fn)
+            b = (torch.randn(size, size, device="cuda") * 0.5).to(torch.float8_e4m3fn).t()
+            one = torch.ones((), device="cuda")
+            flops = 2.0 * size ** 3
+            for _ in range(3):
+                torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            stream.synchronize()
+            best = None
+            for _ in range(10):
+                time.sleep(0.02)
+                start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                start.record(stream)
+                torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+                stop.record(stream)
+                stream.synchronize()
+                elapsed = start.elapsed_time(stop)
+                best = elapsed if best is None else min(best, elapsed)
+            calls = max(20, int(2000.0 / best))
+            start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record(stream)
+            for _ in range(calls):
+                torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+            stop.record(stream)
+            stream.synchronize()
+            sustained_ms = start.elapsed_time(stop) / calls
+        return {"burst": flops / (best * 1e-3) / 1e12, "sustained": flops / (sustained_ms * 1e-3) / 1e12,
+                "how": f"torch._scaled_mm (cuBLASLt) e4m3 x e4m3 -> bf16, {size}^3, per-tensor scales: "
+                       f"best of 10 single calls (burst), {calls} calls back to back (sustained)"}
+    except Exception as error:  # noqa: BLE001 - the probe is optional
+        print(f"fp8 peak probe unavailable: {error}", file=sys.stderr, flush=True)
+        return None
+
 
 def run_gpu(args) -> None:
     import torch
@@ -296,38 +290,62 @@ def run_gpu(args) -> None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        one_step(False)
+    from bench_decode import ClockSampler
+
+    warm_begin, warm_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    one_step(False)
     barrier()
-    begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local_rank) as sampler:
-        barrier()
-        begin_event.record(stream)
-        for _ in range(args.steps):
-            one_step(True)
-        end_event.record(stream)
-        barrier()
-    elapsed_ms = begin_event.elapsed_time(end_event)
+    warm_begin.record(stream)
+    for _ in range(max(args.warmup - 1, 2)):
+        one_step(False)
+    warm_end.record(stream)
+    barrier()
+    estimate_ms = warm_begin.elapsed_time(warm_end) / max(args.warmup - 1, 2)
+    # Repeats of the K-step loop: enough for TIMED_REGION_SECONDS of timed work in total, the same
+    # count on every rank.
+    repeats = max(1, min(2000, math.ceil(TIMED_REGION_SECONDS * 1e3 / max(estimate_ms * args.steps, 1e-3))))
+    if args.repeats > 0:
+        repeats = args.repeats
     if distributed:
-        tensor = torch.tensor([elapsed_ms], device=device)
+        tensor = torch.tensor([repeats], device=device)
         dist.all_reduce(tensor, op=dist.ReduceOp.MAX)
-        elapsed_ms = float(tensor.item())
-    ms_per_step = elapsed_ms / args.steps
+        repeats = int(tensor.item())
+    # Plain repeats give `value`; after every fourth one an extra repeat carries an event pair
+    # around every GEMM launch (the roofline's per-kernel durations), so that those events do not
+    # sit inside the regions `value` is taken from.
+    regions, instrumented = [], 0
+    with ClockSampler(local_rank) as sampler:
+        for repeat in range(repeats):
+            begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            barrier()
+            begin_event.record(stream)
+            for _ in range(args.steps):
+                one_step(False)
+            end_event.record(stream)
+            barrier()
+            regions.append((begin_event, end_event))
+            if repeat % 4 == 0:
+                for _ in range(args.steps):
+                    one_step(True)
+                barrier()
+                instrumented += 1
+    region_ms = torch.tensor([begin.elapsed_time(end) for begin, end in regions], device=device)
+    if distributed:
+        dist.all_reduce(region_ms, op=dist.ReduceOp.MAX)      # each repeat: the slowest rank
+    region_ms = region_ms.tolist()
+    ms_per_step = statistics.median(region_ms) / args.steps
     value = step_flops() / (ms_per_step * 1e-3) / 1e12
+    clocks = sampler.summary()
 
     gemm_ms = sum(start.elapsed_time(stop) for _, start, stop in gemm_events)
     per_layer = {}
     for name, start, stop in gemm_events:
         per_layer.setdefault(name, []).append(start.elapsed_time(stop))
     local_flops = sum(2.0 * TOKENS * layer["local_n"] * layer["k"] for layer in layers)
-    achieved = local_flops * args.steps / (gemm_ms * 1e-3) / 1e12
+    achieved = local_flops * args.steps * instrumented / (gemm_ms * 1e-3) / 1e12
     peaks = measured_peaks()
-    if "bf16_tflops_sustained" in peaks:
-        peak = 2.0 * float(peaks["bf16_tflops_sustained"])
-        peak_note = "2 x measured sustained bf16 cuBLAS TFLOP/s (FP8 issues at twice the bf16 rate)"
-    else:
-        peak = 2.0 * 1400.0
-        peak_note = "2 x fallback sustained bf16 1.4 PFLOP/s"
+    probe = fp8_peak_probe(torch, stream) if (world == 1 and not args.no_peak_probe) else None
+    begin_event, end_event = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
 
     # ------------------------------------------------------------------ end-to-end leg
     e2e_steps = max(1, min(args.steps, 10))
@@ -412,10 +430,104 @@ def run_gpu(args) -> None:
         e2e_ms = float(tensor.item())
     e2e_value = step_flops() / (e2e_ms / e2e_steps * 1e-3) / 1e12
 
+    # ------------------------------------------------ decode GEMV and reference-kernel legs
+    decode_record, reference_records = None, None
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+    hbm_source = ("measured copy bandwidth (MEASURED_PEAKS.json)" if "hbm_gbs" in peaks
+                  else "fallback 6650 GB/s (an earlier measurement on this pool)")
+    if world == 1 and not args.no_decode:
+        import bench_decode
+        with ClockSampler(local_rank) as decode_sampler:
+            results = bench_decode.run(["nvfp4"], 200, 5, hbm_peak, sampler=decode_sampler, echo=False)["results"]
+        fractions = [record["frac_of_measured_hbm"] for record in results]
+        decode_record = {
+            "op": "bf16 x NVFP4 GEMV (mircuda_b200_nvfp4_vector_*), Qwen3-8B weight shapes, M in {1,4,8}",
+            "method": ("weights rotate through banks larger than 768 MiB, 200 back-to-back launches from a "
+                       "CUDA graph between two events, median of 5 (examples/dense-vector.rs:9,133-141)"),
+            "unit": "GB/s of algorithmic bytes (N*K*0.5625 + M*K*2 + M*N*2)",
+            "peak_gbs": hbm_peak, "peak_source": hbm_source,
+            "min_frac": min(fractions), "mean_frac": sum(fractions) / len(fractions),
+            "clocks": decode_sampler.summary(),
+            "results": [{key: record[key] for key in ("shape", "m", "us", "gbs", "frac_of_measured_hbm",
+                                                      "banks", "sm_mhz", "clock_samples")}
+                        for record in results],
+        }
+    if world == 1 and not args.no_reference_kernels:
+        import bench_decode
+        reference_records = bench_decode.reference_kernel_records(100, 3, hbm_peak)
+
     if rank == 0:
+        timed_ms = sum(region_ms)
+        sustained_regime = timed_ms >= 1000.0
+        candidates = {}
+        if probe is not None:
+            candidates["fp8_probe_burst"] = probe["burst"]
+            candidates["fp8_probe_sustained"] = probe["sustained"]
+        if "bf16_tflops" in peaks:
+            candidates["2x_bf16_burst"] = 2.0 * float(peaks["bf16_tflops"])
+            candidates["2x_bf16_sustained"] = 2.0 * float(peaks["bf16_tflops_sustained"])
+        if probe is not None:
+            peak = probe["sustained"] if sustained_regime else probe["burst"]
+            peak_note = ("measured FP8 tensor peak of this GPU, " + ("sustained" if sustained_regime else "burst")
+                         + f" figure because the timed regions sum to {timed_ms:.0f} ms: " + probe["how"])
+        elif "bf16_tflops" in peaks:
+            peak = candidates["2x_bf16_sustained" if sustained_regime else "2x_bf16_burst"]
+            peak_note = ("2 x measured " + ("sustained" if sustained_regime else "burst")
+                         + " bf16 cuBLAS TFLOP/s of MEASURED_PEAKS.json (no FP8 probe in this run)")
+        else:
+            peak = NOMINAL_FP8_TFLOPS
+            peak_note = "nominal dense FP8 (no measured peak available)"
+        mhz = clocks["sm_mhz"]
+        layer_table = {}
+        for name, times in per_layer.items():
+            layer = next(l for l in layers if l["name"] == name)
+            mean_ms = statistics.mean(times)
+            layer_table[name] = {
+                "us": mean_ms * 1e3,
+                "tflops": 2.0 * TOKENS * layer["local_n"] * layer["k"] / (mean_ms * 1e-3) / 1e12,
+                # time x clock: a kernel change moves it, a clock change does not
+                "us_x_mhz": mean_ms * 1e3 * mhz if mhz else None,
+            }
+        if distributed:
+            received = (world - 1) / world * TOKENS * sum(n for _, n, _ in SHAPES) * 2.0
+            roofline = {
+                "bound": "nvlink", "achieved": received / (ms_per_step * 1e-3) / 1e9,
+                "peak": NVLINK_GBS_PER_DIRECTION, "unit": "GB/s",
+                "frac": received / (ms_per_step * 1e-3) / 1e9 / NVLINK_GBS_PER_DIRECTION,
+                "traffic": None,
+                "kernel": "block_scaled_pair_gemm_kernel (gather epilogue)",
+                "peak_source": ("nominal NVLink 5 ingress per GPU; measured on this pool: 770 GB/s peer copy, "
+                                "555 GB/s for SM-issued peer stores"),
+                "bytes_received_per_rank_per_step": received,
+                "why": ("every rank must receive the other ranks' columns of all four outputs; with K = 4096 "
+                        "that is one received byte per 4096 flop, so from 2 GPUs up the step is bound by "
+                        "NVLink ingress, not by the tensor pipe"),
+                "gemm_tflops_this_rank": achieved, "per_layer": layer_table,
+            }
+        else:
+            roofline = {
+                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                "frac": achieved / peak,
+                # dram__bytes_read.sum + dram__bytes_write.sum of the gate_up launch from the ncu
+                # capture summarised under profiles/ (algorithmic 322.5 MB; 33 MB of C were still
+                # dirty in L2 when the kernel ended). Not measured by this run.
+                "traffic": 289.6e6, "traffic_launch": "gate_up (M=4096, N=24576, K=4096)",
+                "traffic_source": "profiles/block_scaled_pair_gemm_kernel_gate_up_4096x24576x4096.md",
+                "kernel": "block_scaled_pair_gemm_kernel",
+                "peak_source": peak_note,
+                "frac_of": {name: achieved / figure for name, figure in candidates.items()},
+                "peaks_tflops": candidates,
+                "frac_of_nominal_fp8_4500": achieved / NOMINAL_FP8_TFLOPS,
+                "value_frac_of_nominal_fp8_4500": value / NOMINAL_FP8_TFLOPS,
+                "per_layer": layer_table,
+                "per_layer_tflops": {name: entry["tflops"] for name, entry in layer_table.items()},
+            }
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": args.warmup, "ms_per_step": ms_per_step,
+            "ms_per_step_min": min(region_ms) / args.steps, "ms_per_step_max": max(region_ms) / args.steps,
+            "repeats": repeats, "timed_ms_total": timed_ms,
+            "higher_is_better": True,
             "scaling": "strong", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate)",
             "data": "synthetic",
             "config": {
@@ -428,26 +540,25 @@ def run_gpu(args) -> None:
                                 f"weight N column-sharded x{world}, NCCL all-gather of outputs"
                                 if distributed else "single GPU"),
                 "l2": "per-step operands (193 MB of weights + activations + 318 MB of outputs) exceed the 126 MB L2",
+                "timing": (f"the {args.steps}-step loop timed {repeats} times back to back (barrier + synchronize "
+                           "around each), ms_per_step = median repeat / steps, max over ranks per repeat"),
             },
-            "roofline": {
-                "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                "frac": achieved / peak,
-                # dram__bytes_read.sum + dram__bytes_write.sum of the gate_up launch from the ncu
-                # capture summarised under profiles/ (algorithmic 322.5 MB; 33 MB of C were still
-                # dirty in L2 when the kernel ended). Not measured by this run.
-                "traffic": 289.6e6, "traffic_launch": "gate_up (M=4096, N=24576, K=4096)",
-                "kernel": "block_scaled_pair_gemm_kernel",
-                "peak_source": peak_note, "frac_of_nominal_fp8_4500": achieved / 4500.0,
-                "per_layer_tflops": {
-                    name: 2.0 * TOKENS * next(l for l in layers if l["name"] == name)["local_n"]
-                    * next(l for l in layers if l["name"] == name)["k"] / (statistics.mean(times) * 1e-3) / 1e12
-                    for name, times in per_layer.items()},
-            },
+            "roofline": roofline,
             "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            # launches of this library's kernels inside one timed region of `steps` steps
             "gpu_launches": args.steps * 2 * len(layers),
-            "clocks": sampler.summary(),
+            "clocks": clocks,
         }
+        if decode_record is not None:
+            line["decode"] = decode_record
+        if reference_records is not None:
+            line["reference_kernels"] = {
+                "what": ("the reference's own kernels that run on sm_100a (built from its sources into "
+                         "oracle/_ref, reference launch geometry) timed beside this library's kernel for the "
+                         "same op and inputs; rotating banks, CUDA-graph launches, median of 3"),
+                "results": reference_records,
+            }
         if world == 1 and not args.no_cpu_baseline:
             line["cpu_baseline"] = cpu_baseline_leg()
         print(json.dumps(line), flush=True)
@@ -460,11 +571,17 @@ def main() -> None:
     global SHAPES
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
-    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--steps", type=int, default=100)
     parser.add_argument("--warmup", type=int, default=5)
     parser.add_argument("--impl", default="b200", choices=["b200", "reference"])
     parser.add_argument("--no-cpu-baseline", action="store_true")
     parser.add_argument("--no-e2e", action="store_true", help="skip the host-buffer leg (profiling runs)")
+    parser.add_argument("--no-decode", action="store_true", help="skip the decode GEMV record")
+    parser.add_argument("--no-reference-kernels", action="store_true",
+                        help="skip timing the reference's own kernels from oracle/_ref")
+    parser.add_argument("--no-peak-probe", action="store_true", help="skip the cuBLASLt FP8 peak probe")
+    parser.add_argument("--repeats", type=int, default=0,
+                        help="repeats of the timed --steps loop (default: enough for about 2 s)")
     parser.add_argument("--layers", default=",".join(name for name, _, _ in SHAPES),
                         help="comma-separated subset of the four linears (profiling runs)")
     args = parser.parse_args()

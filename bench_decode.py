@@ -1,6 +1,6 @@
 """Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
 
-    python -m mircuda_b200.bench_decode [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8,marlin_moe]
+    python bench_decode.py [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8,marlin_moe]
 
 Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
 examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
@@ -18,11 +18,18 @@ import argparse
 import ctypes
 import json
 import math
+import os
 import statistics
+import threading
+
+import sys
+from pathlib import Path
 
 import torch
 
-from . import _lib, plans
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from mircuda_b200 import _lib, plans  # noqa: E402
 
 SHAPES = [("qkv", 6144, 4096), ("o", 4096, 4096), ("gate_up", 24576, 4096), ("down", 4096, 12288)]
 BANK_BYTES = 768 << 20
@@ -30,6 +37,80 @@ BANK_BYTES = 768 << 20
 
 def _banks(bytes_per_bank: int) -> int:
     return max(8, math.ceil(BANK_BYTES / bytes_per_bank))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons through NVML while a timed region runs (read-only
+    queries every few milliseconds; `nvidia-smi` would take ~100 ms a call). NVML is initialised
+    and the device handle fetched before the region starts, so the first sample lands inside."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
+
+    def __init__(self, index: int, interval: float = 0.004):
+        self.index, self.interval = index, interval
+        self.clocks: list[int] = []
+        self.power: list[float] = []
+        self.maximum = None
+        self.reasons: set[str] = set()
+        self._handle = None
+        self._nvml = None
+        self._stop = threading.Event()
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            if visible:
+                entry = visible.split(",")[index].strip()
+                index = int(entry) if entry.isdigit() else index
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.maximum = int(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
+        except Exception:  # noqa: BLE001 - no NVML: the record says so (samples 0)
+            self._handle = None
+
+    def sample(self) -> None:
+        if self._handle is None:
+            return
+        nvml = self._nvml
+        try:
+            self.clocks.append(int(nvml.nvmlDeviceGetClockInfo(self._handle, nvml.NVML_CLOCK_SM)))
+            mask = int(nvml.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            for bit, name in self.REASONS.items():
+                if mask & bit:
+                    self.reasons.add(name)
+            self.power.append(nvml.nvmlDeviceGetPowerUsage(self._handle) / 1000.0)
+        except Exception:  # noqa: BLE001
+            pass
+
+    def _run(self):
+        while not self._stop.is_set():
+            self.sample()
+            self._stop.wait(self.interval)
+
+    def __enter__(self):
+        self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        self._thread.join(timeout=10)
+
+    def mark(self) -> int:
+        """Index of the next sample: `summary(start=mark)` then covers what follows."""
+        return len(self.clocks)
+
+    def summary(self, start: int = 0) -> dict:
+        clocks, power = self.clocks[start:], self.power[start:]
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_min_mhz": min(clocks) if clocks else None,
+            "sm_max_mhz": self.maximum,
+            "power_w": statistics.median(power) if power else None,
+            "reasons": sorted(self.reasons),
+            "samples": len(clocks),
+        }
 
 
 def _time(stream, launch, banks: int, cycles: int, repeats: int) -> float:
@@ -145,7 +226,7 @@ W4A16_SHAPES = [("k4096_n14336", 14336, 4096), ("k14336_n4096", 4096, 14336)]
 
 def bench_w4a16(stream, n, k, m, cycles, repeats):
     """int4-g128 weights, f16 activations (the Marlin-style W4A16 shapes of the benchmark)."""
-    from . import dense
+    from mircuda_b200 import dense
     banks = _banks(n * k // 2 + n * k // 128 * 2)
     weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
     scales = [(torch.rand(n * k // 128, device="cuda") * 0.01 + 0.002).to(torch.float16)
@@ -215,7 +296,7 @@ def bench_marlin_moe(stream, n, k, m, cycles, repeats):
 
 def bench_scaled_fp8(stream, n, k, m, cycles, repeats):
     """E4M3 weights and activations, fp32 token scales, fp32 channel scales, bf16 bias."""
-    from . import dense
+    from mircuda_b200 import dense
     banks = _banks(n * k)
     weights = [_random_bytes(n * k, 0x20, 0x48) for _ in range(banks)]
     x = _random_bytes(m * k, 0x20, 0x48)
@@ -232,7 +313,8 @@ def bench_scaled_fp8(stream, n, k, m, cycles, repeats):
     return seconds, n * k + m * k + m * n * 2 + n * 6 + m * 4, banks
 
 
-def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None) -> dict:
+def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None, sampler=None,
+        echo: bool = True) -> dict:
     torch.cuda.set_device(0)
     stream = torch.cuda.Stream()
     results = []
@@ -246,6 +328,7 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                       [1, 8, 64] if op == "marlin_moe" else [1]):
                 if tokens and m not in tokens:
                     continue
+                mark = sampler.mark() if sampler is not None else 0
                 with torch.cuda.stream(stream):
                     if op == "nvfp4":
                         seconds, byte_count, banks = bench_nvfp4(stream, n, k, m, cycles, repeats)
@@ -267,9 +350,147 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                           byte_count / seconds / 1e9 / peak_gbs, "banks": banks}
                 if op in ("w4a16", "scaled_fp8"):
                     record["tflops"] = 2.0 * m * n * k / seconds / 1e12
+                if sampler is not None:
+                    clocks = sampler.summary(mark)
+                    record["sm_mhz"] = clocks["sm_mhz"]
+                    record["clock_samples"] = clocks["samples"]
                 results.append(record)
-                print(json.dumps(record), flush=True)
+                if echo:
+                    print(json.dumps(record), flush=True)
     return {"results": results}
+
+
+# --------------------------------------------------------------- the reference's own kernels
+# The reference kernels that compile for sm_100a (plain SIMT, no waits): FP4 x FP4 GEMV and dense
+# GEMV (sys/native/{fp4_vector,dense_vector}_sm120.cu), the MXFP8 activation quantizer and the
+# weight-only MXFP8 product (kernels/mxfp8.cu:69-96,111-217), built from the reference's sources
+# into oracle/_ref by oracle/build.py and launched with the reference's own geometry. They are
+# timed beside this library's kernels for the same op, same inputs, same rotating banks.
+
+REF_DIR = Path(__file__).resolve().parent / "oracle" / "_ref"
+
+
+def _reference_library(name: str):
+    path = REF_DIR / f"libref_{name}.so"
+    return ctypes.CDLL(str(path)) if path.exists() else None
+
+
+def reference_kernel_records(cycles: int, repeats: int, peak_gbs: float) -> list[dict]:
+    torch.cuda.set_device(0)
+    stream = torch.cuda.Stream()
+    handle = ctypes.c_void_p(stream.cuda_stream)
+    pointer = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    records = []
+    vector, device = _reference_library("vector"), _reference_library("device")
+
+    def add(op, shape, byte_count, ours, reference):
+        records.append({"op": op, "shape": shape, "us": ours * 1e6, "reference_us": reference * 1e6,
+                        "speedup_over_reference_kernel": reference / ours,
+                        "frac_of_measured_hbm": byte_count / ours / 1e9 / peak_gbs,
+                        "reference_frac_of_measured_hbm": byte_count / reference / 1e9 / peak_gbs})
+
+    with torch.cuda.stream(stream):
+        if vector is not None:
+            vector.mircuda_fp4_vector_execute.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_float]
+            vector.mircuda_fp4_vector_destroy.argtypes = [ctypes.c_void_p]
+            vector.mircuda_dense_vector_execute.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_float] * 2
+            vector.mircuda_dense_vector_destroy.argtypes = [ctypes.c_void_p]
+            for name, n, k in SHAPES:
+                # FP4 x FP4 GEMV
+                scale_bytes = (n + 127) // 128 * (k // 64) * 512
+                banks = _banks(n * k // 2 + scale_bytes)
+                weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+                scales = [_random_bytes(scale_bytes, 0x28, 0x48) for _ in range(banks)]
+                x, xs = _random_bytes(k // 2, 0, 256), _random_bytes((k // 64) * 512, 0x28, 0x48)
+                out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+                plan = plans.BlockScaledFp4VectorPlan(stream, plans.BlockScaledFp4VectorSpec(n, k))
+                raw = ctypes.c_void_p()
+                if vector.mircuda_fp4_vector_create(n, k, handle, ctypes.byref(raw)) != 0:
+                    raise RuntimeError("reference fp4_vector plan")
+                torch.cuda.synchronize()
+                ours = _time(stream, lambda i: plan.execute(stream, x, xs, weights[i], scales[i], out, 0.5),
+                             banks, cycles, repeats)
+
+                def reference_fp4(i):
+                    if vector.mircuda_fp4_vector_execute(raw, handle, pointer(x), pointer(xs), pointer(weights[i]),
+                                                         pointer(scales[i]), pointer(out), 0.5) != 0:
+                        raise RuntimeError("reference fp4_vector execute")
+
+                reference = _time(stream, reference_fp4, banks, cycles, repeats)
+                plan.close()
+                vector.mircuda_fp4_vector_destroy(raw)
+                add("fp4_vector", name, n * k * 0.5625 + k * 0.5625 + n * 2, ours, reference)
+                del weights, scales
+                torch.cuda.empty_cache()
+                # dense bf16 GEMV
+                banks = _banks(n * k * 2)
+                weights = [(torch.randn(n * k, device="cuda") * 0.02).to(torch.bfloat16) for _ in range(banks)]
+                xd = torch.randn(k, device="cuda").to(torch.bfloat16)
+                plan = plans.DenseVectorPlan(stream, plans.DenseVectorSpec(n, k, 1))
+                raw = ctypes.c_void_p()
+                if vector.mircuda_dense_vector_create(1, n, k, handle, ctypes.byref(raw)) != 0:
+                    raise RuntimeError("reference dense_vector plan")
+                torch.cuda.synchronize()
+                ours = _time(stream, lambda i: plan.execute(stream, xd, weights[i], out, 1.0, 0.0),
+                             banks, cycles, repeats)
+
+                def reference_dense(i):
+                    if vector.mircuda_dense_vector_execute(raw, handle, pointer(xd), pointer(weights[i]),
+                                                           pointer(out), 1.0, 0.0) != 0:
+                        raise RuntimeError("reference dense_vector execute")
+
+                reference = _time(stream, reference_dense, banks, cycles, repeats)
+                plan.close()
+                vector.mircuda_dense_vector_destroy(raw)
+                add("dense_vector_bf16", name, 2.0 * n * k + 2 * k + 2 * n, ours, reference)
+                del weights
+                torch.cuda.empty_cache()
+        if device is not None:
+            u32 = ctypes.c_uint32
+            device.ref_mxfp8_quantize_bf16.argtypes = [ctypes.c_void_p] * 3 + [u32, u32, ctypes.c_void_p]
+            device.ref_mxfp8_bf16.argtypes = [ctypes.c_void_p] * 4 + [u32, u32, u32, ctypes.c_int, ctypes.c_void_p]
+            for rows, columns in ((4096, 4096), (4096, 12288)):
+                # activation quantizer: inputs rotate through banks larger than L2
+                byte_count = rows * columns * (2 + 1 + 1 / 32)
+                banks = max(8, math.ceil((256 << 20) / (rows * columns * 2)))
+                values = [torch.randn(rows, columns, device="cuda").to(torch.bfloat16) for _ in range(banks)]
+                codes = torch.empty(rows * columns, dtype=torch.uint8, device="cuda")
+                scales = torch.zeros(plans.scale_bytes(rows, columns // 32), dtype=torch.uint8, device="cuda")
+                torch.cuda.synchronize()
+                ours = _time(stream, lambda i: plans.mxfp8_quantize_bf16(stream, values[i], codes, scales),
+                             banks, min(cycles, 50), repeats)
+
+                def reference_quantize(i):
+                    if device.ref_mxfp8_quantize_bf16(pointer(values[i]), pointer(codes), pointer(scales), rows,
+                                                      columns, handle) != 0:
+                        raise RuntimeError("reference quantizer launch")
+
+                reference = _time(stream, reference_quantize, banks, min(cycles, 50), repeats)
+                add("mxfp8_quantize_bf16", f"{rows}x{columns}", byte_count, ours, reference)
+                del values
+                torch.cuda.empty_cache()
+            for name, n, k in SHAPES:
+                # weight-only MXFP8 product, one token (kernels/mxfp8.cu:111-153)
+                banks = _banks(n * k + n * k // 32)
+                weights = [_random_bytes(n * k, 0x20, 0x48) for _ in range(banks)]
+                row_scales = [_random_bytes(n * k // 32, 120, 130) for _ in range(banks)]
+                xd = torch.randn(k, device="cuda").to(torch.bfloat16)
+                out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+                operation = plans.MxFp8Matmul(plans.MxFp8Spec(1, k, n))
+                torch.cuda.synchronize()
+                ours = _time(stream, lambda i: operation.execute(stream, xd, weights[i], row_scales[i], out),
+                             banks, cycles, repeats)
+
+                def reference_matmul(i):
+                    if device.ref_mxfp8_bf16(pointer(xd), pointer(weights[i]), pointer(row_scales[i]), pointer(out),
+                                             1, k, n, 0, handle) != 0:
+                        raise RuntimeError("reference weight-only launch")
+
+                reference = _time(stream, reference_matmul, banks, cycles, repeats)
+                add("mxfp8_bf16_weight_only", name, n * k * (1 + 1 / 32) + 2 * k + 2 * n, ours, reference)
+                del weights, row_scales
+                torch.cuda.empty_cache()
+    return records
 
 
 def main() -> None:
@@ -280,7 +501,12 @@ def main() -> None:
     parser.add_argument("--peak-gbs", type=float, default=6551.4)
     parser.add_argument("--shapes", default="", help="subset of qkv,o,gate_up,down (profiling runs)")
     parser.add_argument("--tokens", default="", help="subset of 1,4,8 (profiling runs)")
+    parser.add_argument("--reference-kernels", action="store_true",
+                        help="also time the reference's own sm_100a-runnable kernels (oracle/_ref)")
     args = parser.parse_args()
+    if args.reference_kernels:
+        for record in reference_kernel_records(args.cycles, args.repeats, args.peak_gbs):
+            print(json.dumps(record), flush=True)
     summary = run(args.ops.split(","), args.cycles, args.repeats, args.peak_gbs,
                   set(filter(None, args.shapes.split(","))),
                   {int(t) for t in args.tokens.split(",") if t})

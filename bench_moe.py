@@ -1,9 +1,9 @@
 """Grouped MoE benchmark: Qwen3-30B-A3B-shaped feed-forward (128 experts, top-8, hidden 2048,
 expert intermediate 768, 4096 tokens) as bf16 and as NVFP4, experts sharded over the GPUs.
 
-    python -m mircuda_b200.bench_moe [--mode bf16|nvfp4|both] [--steps K] [--warmup W]
+    python bench_moe.py [--mode bf16|nvfp4|both] [--steps K] [--warmup W]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
-        -m mircuda_b200.bench_moe --mode bf16
+        bench_moe.py --mode bf16
 
 Inputs are synthetic and seeded (seed 5000 + index): activations N(0,1), expert weights
 N(0,0.02), router logits N(0,1) -> softmax -> top-8 -> renormalised. The total token count is
@@ -25,7 +25,12 @@ import os
 import torch
 import torch.distributed as dist
 
-from . import moe
+import sys
+from pathlib import Path
+
+sys.path.insert(0, str(Path(__file__).resolve().parent))
+
+from mircuda_b200 import moe  # noqa: E402
 
 EXPERTS, TOP_K, HIDDEN, INTERMEDIATE, TOKENS = 128, 8, 2048, 768, 4096
 

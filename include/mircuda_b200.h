@@ -290,15 +290,24 @@ int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* rows, unsign
  * remote_row[i]. collect_rows sums, for every token, weights[t, j] * (row remote_row[slot[t, j]]
  * of the owner's result buffer). The caller orders these launches against the peers with its
  * own barriers; no kernel here waits for another GPU. */
+/* Capacity: every rank's receive and result buffers hold `capacity_rows` rows (the same on
+ * all ranks). Routing decides at run time how many rows an owner receives, so the bound is
+ * enforced on the device: expert_layout clamps rows[] / offsets[] / *received_rows to it and
+ * sets *overflow (a device-visible word, may be null) to 1 on every rank that sees an expert
+ * run past it; dispatch_rows does not send a row at or past it and records -1 for it;
+ * collect_rows adds nothing for a row recorded as -1. No access leaves the buffers; the
+ * caller turns a raised word into an error. */
 int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
                                    uint32_t experts, uint32_t align, int* base_for_me,
                                    unsigned int* rows, unsigned int* offsets,
-                                   unsigned int* received_rows, void* stream);
+                                   unsigned int* received_rows, uint32_t capacity_rows,
+                                   unsigned int* overflow, void* stream);
 int mircuda_b200_moe_dispatch_rows_bf16(const void* source, const int* source_index,
                                         const int* sorted_expert, const int* position,
                                         const int* base_for_me, void* const* receive_buffers,
                                         uint32_t world, int* remote_row, uint32_t count,
-                                        uint32_t local_experts, uint32_t columns, void* stream);
+                                        uint32_t local_experts, uint32_t columns,
+                                        uint32_t capacity_rows, void* stream);
 /* Row-major scale bytes [rows, columns] (as dispatched) -> the 128-row x 4-column atoms the
  * block-scaled plans read, for the first min(rows, *row_bound) rows (row_bound may be null);
  * columns % 16 == 0. Same permutation as mircuda_b200_mxfp8_swizzle_scales, 16 bytes a thread. */

@@ -66,9 +66,9 @@ SIGNATURES.update({
     "mircuda_b200_moe_swiglu_bf16": (_i, [_vp, _vp, _u32, _vp, _u32, _vp]),
     "mircuda_b200_moe_combine_rows_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mircuda_b200_moe_group_offsets": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
-    "mircuda_b200_moe_expert_layout": (_i, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _vp]),
+    "mircuda_b200_moe_expert_layout": (_i, [_vp, _u32, _u32, _u32, _u32, _vp, _vp, _vp, _vp, _u32, _vp, _vp]),
     "mircuda_b200_nvfp4_quantize_rows_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),
-    "mircuda_b200_moe_dispatch_rows_bf16": (_i, [_vp] * 5 + [_vpp, _u32, _vp, _u32, _u32, _u32, _vp]),
+    "mircuda_b200_moe_dispatch_rows_bf16": (_i, [_vp] * 5 + [_vpp, _u32, _vp, _u32, _u32, _u32, _u32, _vp]),
     "mircuda_b200_moe_collect_rows_bf16": (_i, [_vpp, _u32, _vp, _vp, _vp, _vp, _vp, _u32, _u32, _u32, _u32, _vp]),
     "mircuda_marlin_nvfp4_moe_execute": (_i, [_vp] * 11 + [_i, _b, _i, _i, _i, _i, _vp, _b]),
     "mircuda_marlin_mxfp4_moe_execute": (_i, [_vp] * 10 + [_i, _b, _i, _i, _i, _i, _vp, _b]),

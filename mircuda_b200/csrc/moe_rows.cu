@@ -128,11 +128,15 @@ __global__ void moe_group_offsets_kernel(const int* __restrict__ counts, unsigne
 //                     128 to keep NVFP4 scale tiles per expert)
 //   base_for_me[e]  = start[e] + rows of sources before `rank`  (where this rank's rows go)
 //   rows/offsets    = the grouped plans' arrays for this rank's own experts
+//   capacity_rows   = rows of every rank's receive buffer: an owner's rows / offsets are clamped
+//                     to it (rows past it are neither dispatched nor computed) and `overflow`
+//                     is raised on every rank that sees an expert run past it
 __global__ void moe_expert_layout_kernel(const int* __restrict__ all_counts, uint32_t world,
                                          uint32_t rank, uint32_t experts, uint32_t local_experts,
                                          uint32_t align, int* __restrict__ base_for_me, unsigned int* __restrict__ rows,
                                          unsigned int* __restrict__ offsets,
-                                         unsigned int* __restrict__ received_rows) {
+                                         unsigned int* __restrict__ received_rows,
+                                         uint32_t capacity_rows, unsigned int* __restrict__ overflow) {
   extern __shared__ uint32_t totals[];
   const uint32_t expert = threadIdx.x;
   uint32_t total = 0u, before_me = 0u;
@@ -152,11 +156,13 @@ __global__ void moe_expert_layout_kernel(const int* __restrict__ all_counts, uin
     start += (totals[other] + align - 1u) / align * align;
   }
   base_for_me[expert] = static_cast<int>(start + before_me);
+  if (start + total > capacity_rows && overflow != nullptr) *overflow = 1u;
   if (expert / local_experts == rank) {
-    rows[expert - owner_first] = total;
-    offsets[expert - owner_first] = start;
+    const uint32_t clamped_start = min(start, capacity_rows);
+    rows[expert - owner_first] = min(total, capacity_rows - clamped_start);
+    offsets[expert - owner_first] = clamped_start;
     if (expert - owner_first + 1u == local_experts && received_rows != nullptr) {
-      *received_rows = start + (total + align - 1u) / align * align;
+      *received_rows = min(start + (total + align - 1u) / align * align, capacity_rows);
     }
   }
 }
@@ -174,13 +180,19 @@ moe_dispatch_rows_kernel(const uint4* __restrict__ source, const int* __restrict
                          const int* __restrict__ sorted_expert, const int* __restrict__ position,
                          const int* __restrict__ base_for_me, const PeerBases receive,
                          int* __restrict__ remote_row, uint32_t count, uint32_t local_experts,
-                         uint32_t pieces) {
+                         uint32_t pieces, uint32_t capacity_rows) {
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t item = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; item < count; item += warps) {
     const int expert = __ldg(sorted_expert + item);
     const uint32_t owner = static_cast<uint32_t>(expert) / local_experts;
     const int row = __ldg(base_for_me + expert) + __ldg(position + item);
+    // A row at or past the owner's capacity is not sent (the layout kernel has raised the
+    // overflow word and the owner computes nothing for it); -1 tells the way back to skip it.
+    if (row < 0 || static_cast<uint32_t>(row) >= capacity_rows) {
+      if (lane == 0) remote_row[item] = -1;
+      continue;
+    }
     if (lane == 0) remote_row[item] = row;
     const uint4* in = source + static_cast<size_t>(__ldg(source_index + item)) * pieces;
     uint4* out = static_cast<uint4*>(receive.base[owner]) + static_cast<size_t>(row) * pieces;
@@ -207,8 +219,11 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
     if (lane < top_k) {
       const int item = __ldg(slot + token * top_k + lane);
       const uint32_t owner = static_cast<uint32_t>(__ldg(sorted_expert + item)) / local_experts;
-      my_row = static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(remote_row[item]) * pieces;
-      my_weight = __ldg(weights + token * top_k + lane);
+      const int row = remote_row[item];
+      if (row >= 0) {       // a row that did not fit the owner's buffer contributes nothing
+        my_row = static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(row) * pieces;
+        my_weight = __ldg(weights + token * top_k + lane);
+      }
     }
     for (uint32_t piece = lane; piece < pieces; piece += 32u) {
       uint4 values[TOP_K];
@@ -218,7 +233,8 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
         const uint4* row = reinterpret_cast<const uint4*>(
             __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), choice));
         scale[choice] = __shfl_sync(0xffffffffu, my_weight, choice);
-        values[choice] = static_cast<uint32_t>(choice) < top_k ? row[piece] : make_uint4(0u, 0u, 0u, 0u);
+        values[choice] = (static_cast<uint32_t>(choice) < top_k && row != nullptr) ? row[piece]
+                                                                                   : make_uint4(0u, 0u, 0u, 0u);
       }
       float sums[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -342,28 +358,29 @@ extern "C" int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* r
 extern "C" int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
                                               uint32_t experts, uint32_t align, int* base_for_me,
                                               unsigned int* rows, unsigned int* offsets,
-                                              unsigned int* received_rows, void* stream) {
+                                              unsigned int* received_rows, uint32_t capacity_rows,
+                                              unsigned int* overflow, void* stream) {
   using namespace mircuda_b200::moe_rows;
   if (all_counts == nullptr || base_for_me == nullptr || rows == nullptr || offsets == nullptr ||
       world == 0 || world > 8 || rank >= world || experts == 0 || experts > 1024 ||
-      experts % world != 0 || align == 0) {
+      experts % world != 0 || align == 0 || capacity_rows == 0 || capacity_rows > 0x7fffffffu) {
     return -1;
   }
   moe_expert_layout_kernel<<<1, experts, experts * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
       all_counts, world, rank, experts, experts / world, align, base_for_me, rows, offsets,
-      received_rows);
+      received_rows, capacity_rows, overflow);
   return static_cast<int>(cudaPeekAtLastError());
 }
 
 extern "C" int mircuda_b200_moe_dispatch_rows_bf16(
     const void* source, const int* source_index, const int* sorted_expert, const int* position,
     const int* base_for_me, void* const* receive_buffers, uint32_t world, int* remote_row,
-    uint32_t count, uint32_t local_experts, uint32_t columns, void* stream) {
+    uint32_t count, uint32_t local_experts, uint32_t columns, uint32_t capacity_rows, void* stream) {
   using namespace mircuda_b200::moe_rows;
   if (source == nullptr || source_index == nullptr || sorted_expert == nullptr ||
       position == nullptr || base_for_me == nullptr || receive_buffers == nullptr ||
       remote_row == nullptr || world == 0 || world > 8 || local_experts == 0 || columns == 0 ||
-      columns % 8 != 0 || !aligned16(source)) {
+      columns % 8 != 0 || !aligned16(source) || capacity_rows == 0 || capacity_rows > 0x7fffffffu) {
     return -1;
   }
   PeerBases receive = {};
@@ -375,7 +392,7 @@ extern "C" int mircuda_b200_moe_dispatch_rows_bf16(
   moe_dispatch_rows_kernel<<<grid_for(count, kThreads / 32), kThreads, 0,
                              static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(source), source_index, sorted_expert, position, base_for_me, receive,
-      remote_row, count, local_experts, columns / 8u);
+      remote_row, count, local_experts, columns / 8u, capacity_rows);
   return static_cast<int>(cudaPeekAtLastError());
 }
 

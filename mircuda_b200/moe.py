@@ -36,6 +36,10 @@ import torch.distributed as dist
 from . import _lib, plans, plans_fp4
 
 
+class CapacityExceeded(RuntimeError):
+    """The routing sent a rank more rows than its receive buffers were sized for."""
+
+
 def route(logits: torch.Tensor, top_k: int):
     """Router: softmax over experts, top-k, renormalised weights. Returns (experts [T, k] int64,
     weights [T, k] float32)."""
@@ -234,6 +238,11 @@ class ExpertParallelMoe:
                 groups, capacity, hidden, intermediate, rows, self.local_experts))
         self.gemm_events = None   # set to a list to record (name, start, stop) CUDA events
         self.static_scales = False
+        # Raised by the layout kernel when the routing sends an owner more rows than its buffers
+        # hold. Pinned host memory: kernels write it through its device-visible address and the
+        # host reads it without touching the stream.
+        self._overflow = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self._overflow_pointer = ctypes.c_void_p(self._overflow.data_ptr())
 
     # ------------------------------------------------------------------ helpers
     def _handle(self):
@@ -261,10 +270,29 @@ class ExpertParallelMoe:
             self._handle()))
 
     # ------------------------------------------------------------------- one step
+    def check(self, synchronize: bool = True) -> None:
+        """Raises `CapacityExceeded` if a step since the last check routed more rows to an
+        owner than `capacity` (the overflowing rows were skipped, nothing was written out of
+        bounds, and the outputs of the affected tokens lack those experts' contributions).
+        With `synchronize` the layer's stream is drained first, so the answer covers every
+        enqueued step; without it only steps that have already run are seen."""
+        if synchronize:
+            self.stream.synchronize()
+        if int(self._overflow[0]) != 0:
+            self._overflow[0] = 0
+            raise CapacityExceeded(
+                f"an expert-parallel MoE step needed more than {self.buffer_rows} receive rows on a rank")
+
     def forward(self, x: torch.Tensor, dispatch: Dispatch, routing_weights: torch.Tensor) -> torch.Tensor:
-        """x [tokens, hidden] bf16 on this rank -> output [tokens, hidden] bf16."""
+        """x [tokens, hidden] bf16 on this rank -> output [tokens, hidden] bf16. An overflow of
+        the receive capacity seen on an earlier step raises `CapacityExceeded` here; `check()`
+        reports the current one."""
+        self.check(synchronize=False)
         if self.peer:
             return self._forward_peer(x, dispatch, routing_weights)
+        if dispatch.largest_block > self.capacity:
+            raise CapacityExceeded(
+                f"a destination block needs {dispatch.largest_block} rows, capacity is {self.capacity}")
         lib, handle = self._lib, self._handle()
         assignments = dispatch.source_rows.numel()
         rows = self.world * self.capacity
@@ -360,7 +388,8 @@ class ExpertParallelMoe:
                 all_counts = dispatch.counts
             self._timed("layout", lambda: plans._check(lib.mircuda_b200_moe_expert_layout(
                 self._p(all_counts), self.world, self.rank, self.experts, 128, self._p(self.base_for_me),
-                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle)))
+                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), self.buffer_rows,
+                self._overflow_pointer, handle)))
 
             def dispatch_rows():
                 for source, pointers, units in ((self.token_codes, self._code_pointers, self._code_units),
@@ -369,7 +398,7 @@ class ExpertParallelMoe:
                         self._p(source), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
                         self._p(dispatch.position), self._p(self.base_for_me),
                         ctypes.cast(pointers, pointer_array), self.world, self._p(self.remote_rows),
-                        assignments, self.local_experts, units, handle))
+                        assignments, self.local_experts, units, self.buffer_rows, handle))
                 if self.world > 1:
                     self._codes_symmetric.barrier()
 
@@ -429,12 +458,14 @@ class ExpertParallelMoe:
                 all_counts = dispatch.counts
             plans._check(lib.mircuda_b200_moe_expert_layout(
                 self._p(all_counts), self.world, self.rank, self.experts, 1, self._p(self.base_for_me),
-                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), handle))
+                self._p(self.rows), self._p(self.offsets), self._p(self.received_rows), self.buffer_rows,
+                self._overflow_pointer, handle))
             plans._check(lib.mircuda_b200_moe_dispatch_rows_bf16(
                 self._p(x), self._p(dispatch.source_rows), self._p(dispatch.sorted_experts),
                 self._p(dispatch.position), self._p(self.base_for_me),
                 ctypes.cast(self._receive_pointers, pointer_array), self.world,
-                self._p(self.remote_rows), assignments, self.local_experts, self.hidden, handle))
+                self._p(self.remote_rows), assignments, self.local_experts, self.hidden,
+                self.buffer_rows, handle))
             if self.world > 1:
                 self._received_symmetric.barrier()     # every peer's rows have landed here
             w = self.weights

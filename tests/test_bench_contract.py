@@ -46,8 +46,10 @@ def test_reference_arm_line():
 
 @pytest.mark.gpu
 def test_cuda_arm_line():
-    record = run_bench("--steps", "3", "--warmup", "3", timeout=600)
+    record = run_bench("--steps", "3", "--warmup", "3", "--repeats", "5", timeout=900)
     check_common(record, 3, 3)
+    assert record["repeats"] == 5
+    assert record["ms_per_step_min"] <= record["ms_per_step"] <= record["ms_per_step_max"]
     assert "impl" not in record or record["impl"] != "reference"
     roofline = record["roofline"]
     for key in ("bound", "achieved", "peak", "unit", "frac", "traffic"):
@@ -59,3 +61,11 @@ def test_cuda_arm_line():
     assert record["e2e"]["value"] < record["value"]          # host copies are inside its timed region
     for key in ("sm_mhz", "sm_max_mhz", "reasons"):
         assert key in record["clocks"], key
+    assert record["clocks"]["samples"] >= 1
+    # the other half of the headline metric: decode GEMV bandwidth, 4 shapes x M in {1, 4, 8}
+    decode = record["decode"]
+    assert len(decode["results"]) == 12 and 0.0 < decode["min_frac"] <= decode["mean_frac"] < 1.2
+    assert {entry["m"] for entry in decode["results"]} == {1, 4, 8}
+    # the reference's own kernels beside this library's (present when oracle/_ref was built)
+    for entry in record["reference_kernels"]["results"]:
+        assert entry["us"] > 0 and entry["reference_us"] > 0

@@ -75,7 +75,7 @@ def test_new_entry_points_validate_without_a_gpu(library):
     assert library.mircuda_b200_w4a16_create(1, 128, 100, fake, ctypes.byref(raw)) == -1
     assert library.mircuda_fp8_vector_create(100, 128, fake, ctypes.byref(raw)) == -1
     assert library.mircuda_b200_moe_swiglu_bf16(None, None, 1, None, 8, fake) == -1
-    assert library.mircuda_b200_moe_expert_layout(None, 2, 0, 8, 1, None, None, None, None, fake) == -1
+    assert library.mircuda_b200_moe_expert_layout(None, 2, 0, 8, 1, None, None, None, None, 64, None, fake) == -1
     assert library.mircuda_b200_mxfp8_bf16_gathered(None, None, None, None, None, None, 1, 1, 1, 32, 1, fake) == -1
     assert library.mircuda_marlin_nvfp4_moe_execute(fake, None, None, None, None, None, None, None, None,
                                                     None, None, 1, False, 1, 64, 64, 0, None, False) == -1

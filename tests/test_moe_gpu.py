@@ -280,3 +280,80 @@ def test_scale_atoms_matches_swizzle(cuda_stream):
     assert library.mircuda_b200_moe_scale_atoms(p(source), p(actual), rows, None, columns, handle) == 0
     cuda_stream.synchronize()
     assert torch.equal(actual, expected)
+
+
+def test_dispatch_respects_the_receive_capacity(cuda_stream):
+    """A routing more skewed than the buffers were sized for: the layout kernel clamps the
+    owner's rows / offsets to the capacity and raises the overflow word, the dispatch kernel
+    skips the rows that do not fit (recorded as -1), the rows behind the capacity keep their
+    contents, and the way back adds nothing for a skipped row."""
+    import ctypes
+    from mircuda_b200 import _lib
+    library = _lib.load()
+    experts, columns, capacity, guard = 4, 64, 24, 8
+    counts = [10, 9, 8, 5]                                   # 32 rows wanted, 24 fit
+    assignments = sum(counts)
+    p = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    handle = ctypes.c_void_p(cuda_stream.cuda_stream)
+    i32 = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    all_counts = i32(counts)
+    sorted_expert = i32([e for e, c in enumerate(counts) for _ in range(c)])
+    position = i32([j for c in counts for j in range(c)])
+    source_index = torch.arange(assignments, dtype=torch.int32, device="cuda")
+    source = torch.arange(assignments * columns, dtype=torch.float32, device="cuda").view(assignments, columns)
+    source = (source % 251 + 1).to(torch.bfloat16)
+    receive = torch.full((capacity + guard, columns), -7.0, dtype=torch.bfloat16, device="cuda")
+    base_for_me, remote_row = i32([0] * experts), i32([0] * assignments)
+    rows, offsets, received = i32([0] * experts), i32([0] * experts), i32([0])
+    overflow = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pointers = (ctypes.c_void_p * 1)(receive.data_ptr())
+    torch.cuda.synchronize()
+    assert library.mircuda_b200_moe_expert_layout(p(all_counts), 1, 0, experts, 1, p(base_for_me), p(rows),
+                                                  p(offsets), p(received), capacity, p(overflow), handle) == 0
+    assert library.mircuda_b200_moe_dispatch_rows_bf16(
+        p(source), p(source_index), p(sorted_expert), p(position), p(base_for_me),
+        ctypes.cast(pointers, ctypes.POINTER(ctypes.c_void_p)), 1, p(remote_row), assignments, experts,
+        columns, capacity, handle) == 0
+    cuda_stream.synchronize()
+    assert int(overflow) == 1
+    assert rows.tolist() == [10, 9, 5, 0] and offsets.tolist() == [0, 10, 19, 24] and int(received) == 24
+    expected_rows = [r if r < capacity else -1 for r in range(assignments)]
+    assert remote_row.tolist() == expected_rows
+    assert torch.equal(receive[:capacity], source[:capacity])
+    assert (receive[capacity:] == -7.0).all()                # nothing was written past the capacity
+    # The way back: token t owns assignments 2t and 2t + 1; skipped rows contribute nothing.
+    tokens, top_k = assignments // 2, 2
+    slot = torch.arange(assignments, dtype=torch.int32, device="cuda")
+    weights = torch.full((tokens, top_k), 0.5, dtype=torch.float32, device="cuda")
+    output = torch.full((tokens, columns), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert library.mircuda_b200_moe_collect_rows_bf16(
+        ctypes.cast(pointers, ctypes.POINTER(ctypes.c_void_p)), 1, p(slot), p(sorted_expert), p(remote_row),
+        p(weights), p(output), tokens, top_k, experts, columns, handle) == 0
+    cuda_stream.synchronize()
+    kept = source.float().clone()
+    kept[capacity:] = 0.0
+    expected = 0.5 * (kept[0::2] + kept[1::2])
+    assert torch.equal(output.float(), expected.to(torch.bfloat16).float())
+    # No overflow: the word stays clear.
+    overflow.zero_()
+    assert library.mircuda_b200_moe_expert_layout(p(all_counts), 1, 0, experts, 1, p(base_for_me), p(rows),
+                                                  p(offsets), p(received), 32, p(overflow), handle) == 0
+    cuda_stream.synchronize()
+    assert int(overflow) == 0 and rows.tolist() == counts
+
+
+def test_layer_reports_an_exceeded_capacity(cuda_stream):
+    """The layer turns the device-side overflow word into CapacityExceeded and stays usable."""
+    from mircuda_b200 import moe
+    device = torch.device("cuda", torch.cuda.current_device())
+    x, gate_up, down, logits = make_inputs(device)
+    chosen, weights = moe.route(logits, TOP_K)
+    dispatch = moe.plan_dispatch(chosen, EXPERTS, 1, None, 1)
+    bank = moe.ExpertWeights(cuda_stream, gate_up, down, False)
+    layer = moe.ExpertParallelMoe(cuda_stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, TOKENS, 128, bank)
+    torch.cuda.synchronize()
+    out = layer.forward(x, dispatch, weights)                 # 192 routed rows, room for 128
+    with pytest.raises(moe.CapacityExceeded):
+        layer.check()
+    assert torch.isfinite(out.float()).all()
+    layer.close()
