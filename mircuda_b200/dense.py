@@ -76,7 +76,10 @@ def quantize_int4(weight: torch.Tensor):
     if k % GROUP != 0:
         raise InvalidMatmulShape("k must be a multiple of 128")
     groups = weight.float().view(n, k // GROUP, GROUP)
-    scales = (groups.abs().amax(dim=-1) / 7.0).to(torch.float16)
+    # A device tensor as divisor: dividing by a Python scalar is evaluated as a multiplication by
+    # the rounded reciprocal on CUDA, which is not the IEEE quotient the format is defined with.
+    seven = torch.full((), 7.0, dtype=torch.float32, device=weight.device)
+    scales = torch.div(groups.abs().amax(dim=-1), seven).to(torch.float16)
     safe = torch.where(scales == 0, torch.ones_like(scales), scales).float()
     codes = torch.clamp(torch.round(groups / safe[..., None]) + 8, 0, 15).to(torch.uint8).view(n, k)
     packed = (codes[:, 0::2] | (codes[:, 1::2] << 4)).contiguous()
