@@ -145,7 +145,14 @@ void mircuda_dense_vector_destroy(void* plan);
  * NEW: the decode shape the benchmark configuration names; the reference serves it
  * through its Marlin NVFP4 dense path (src/marlin/execute.rs:109-128), whose numerics
  * (fp32 accumulation, global scale applied before the bf16 round) this follows.
- * Weights and scales use the same layouts as mircuda_fp4_vector_*. k % 64 == 0. */
+ * Weights and scales use the same layouts as mircuda_fp4_vector_*. k % 64 == 0.
+ * Launch overlap: for shapes with n % 128 == 0 and k % 2048 == 0 (the streaming kernel) a launch
+ * may start fetching `weight` and `weight_scales` while earlier work on the stream is still
+ * running (programmatic dependent launch); `input` is read and `output` written only after
+ * that work has completed. Weights and scales must therefore not be written by work still in
+ * flight on the stream when `execute` is called (they are model constants). The environment
+ * variable MIRCUDA_B200_OVERLAP_LAUNCHES=0, read at plan creation, restores fully serialised
+ * launches. */
 int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* stream, void** output);
 int mircuda_b200_nvfp4_vector_execute(void* plan, void* stream, const void* input,
                                       const void* weight, const void* weight_scales,

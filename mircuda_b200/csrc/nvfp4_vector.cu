@@ -34,6 +34,7 @@
 #include <new>
 
 #include "fp4_codec.cuh"
+#include "nvfp4_stream.hpp"
 #include "ptx.cuh"
 #include "ptx_pair.cuh"
 #include "tensor_map.hpp"
@@ -60,6 +61,8 @@ struct Plan {
   int parts;                 // K parts = cluster size along y
   bool overlap_launches;     // programmatic dependent launch (MIRCUDA_B200_OVERLAP_LAUNCHES=1)
   bool direct;               // the kernel without the shared-memory ring
+  bool stream_kernel;        // the persistent streaming kernel of nvfp4_stream.cu
+  nvfp4_stream::Config stream_config;
   int device;
   cudaStream_t stream;
   uint32_t* status;          // pinned; set when a bounded wait ran out
@@ -614,14 +617,34 @@ extern "C" int mircuda_b200_nvfp4_vector_create(int m, int n, int k, void* strea
     delete plan;
     return status;
   }
-  // The direct kernel is the default: measured equal to the ring kernel on the large shapes
-  // and 6-8 % faster on the small ones. MIRCUDA_B200_NVFP4_VECTOR=ring selects the other.
+  // Shapes the persistent streaming kernel covers (whole 128-row scale tiles, K a multiple of
+  // 2048 up to 12288) run on it; all others on the direct kernel, which measured equal to the
+  // ring kernel on large shapes and 6-8 % faster on small ones.
+  // MIRCUDA_B200_NVFP4_VECTOR=stream|direct|ring forces a choice (stream only where eligible).
   const char* kernel_choice = std::getenv("MIRCUDA_B200_NVFP4_VECTOR");
   plan->direct = !(kernel_choice != nullptr && std::strcmp(kernel_choice, "ring") == 0);
-  // Opt-in: with it, this kernel may read its weights while the previous kernel of the stream
-  // is still running, so the caller must not let that kernel write them.
+  const bool forced_other = kernel_choice != nullptr && (std::strcmp(kernel_choice, "ring") == 0 ||
+                                                         std::strcmp(kernel_choice, "direct") == 0);
+  plan->stream_kernel = !forced_other && mircuda_b200::nvfp4_stream::eligible(n, k);
+  if (plan->stream_kernel) {
+    status = mircuda_b200::nvfp4_stream::prepare(&plan->stream_config, n, k);
+    if (status == -1) {
+      plan->stream_kernel = false;      // more tiles per CTA than it keeps running sums for
+    } else if (status != 0) {
+      cudaFreeHost(plan->status);
+      delete plan;
+      return status;
+    }
+  }
+  // Overlapped launches (programmatic dependent launch): the kernel may fetch its weights and
+  // scales while earlier work of the stream is still running, so that work must not write them
+  // (they are model constants); activations are read and outputs written only after it has
+  // completed. On by default for the streaming kernel, where it removes about 2 us of launch gap
+  // and first-byte latency per call (gate_up 15.6 -> 13.7 us, o 5.8 -> 4.4 us); opt-in for the
+  // other two, where it helps single-wave shapes and hurts multi-part ones.
+  // MIRCUDA_B200_OVERLAP_LAUNCHES=0 / 1 forces it off / on.
   const char* overlap = std::getenv("MIRCUDA_B200_OVERLAP_LAUNCHES");
-  plan->overlap_launches = overlap != nullptr && overlap[0] == '1';
+  plan->overlap_launches = overlap != nullptr ? overlap[0] == '1' : plan->stream_kernel;
   if (const char* forced = std::getenv("MIRCUDA_B200_NVFP4_PARTS")) {
     const int value = std::atoi(forced);
     const int stages = (k + kStageK - 1) / kStageK;
@@ -647,6 +670,12 @@ extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const 
   if (((reinterpret_cast<uintptr_t>(weight) | reinterpret_cast<uintptr_t>(weight_scales) |
         reinterpret_cast<uintptr_t>(input)) & 15u) != 0u) {
     return -1;
+  }
+  if (plan->stream_kernel) {
+    if ((reinterpret_cast<uintptr_t>(output) & 1u) != 0u) return -1;
+    return nvfp4_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input, weight,
+                                weight_scales, output, plan->m, plan->n, plan->k, global_scale,
+                                plan->status);
   }
   if (plan->direct) {
     cudaLaunchConfig_t config = {};

@@ -148,10 +148,12 @@ def test_fp4_vector_random(cuda_stream, fp4_vector_kernel, n, k):
 
 # ------------------------------------------------------------------ bf16 x NVFP4 skinny GEMM
 
-@pytest.fixture(params=["ring", "direct"])
+@pytest.fixture(params=["stream", "ring", "direct"])
 def nvfp4_vector_kernel(request, monkeypatch):
-    """Both kernels behind mircuda_b200_nvfp4_vector_*: weights through a TMA-fed shared-memory
-    ring, or loaded straight from global memory; the choice is read when a plan is created."""
+    """The kernels behind mircuda_b200_nvfp4_vector_*: the persistent streaming kernel (shapes
+    with whole 128-row scale tiles and K a multiple of 2048; other shapes fall to the direct
+    kernel), weights through a TMA-fed shared-memory ring, or loaded straight from global
+    memory; the choice is read when a plan is created."""
     monkeypatch.setenv("MIRCUDA_B200_NVFP4_VECTOR", request.param)
     return request.param
 
@@ -162,6 +164,11 @@ def nvfp4_vector_kernel(request, monkeypatch):
     # Shapes whose row tiles are shared between CTAs in every way: a CTA's share of the
     # units starts and ends inside tiles, and covers whole tiles in between.
     (8, 24576, 4096), (1, 24576, 4096), (8, 4096, 12288), (2, 12160, 2112),
+    # Every form of the streaming kernel: one CTA per tile (K = 2048, 6144) or a CTA pair
+    # (K = 4096, 8192, 12288), one to three K chunks per warp, fewer tiles than CTA pairs,
+    # an odd and an even number of tiles per pair, the four benchmark shapes.
+    (1, 256, 2048), (5, 6144, 6144), (8, 128, 8192), (1, 4096, 12288), (4, 6144, 4096),
+    (2, 2432, 4096), (7, 1152, 8192),
 ])
 def test_nvfp4_vector_random(cuda_stream, nvfp4_vector_kernel, m, n, k):
     from mircuda_b200 import plans
