@@ -27,6 +27,7 @@
 
 #include "fp4_codec.cuh"
 #include "fp4_vector_tc.hpp"
+#include "nvfp4_stream.hpp"
 #include "ptx.cuh"
 #include "layout.cuh"
 
@@ -48,6 +49,10 @@ struct Plan {
   float* partials;          // [slices][row_tiles * 128]
   unsigned int* counters;   // [row_tiles], zero between launches
   fp4_vector_tc::Plan* tensor;   // the tensor-core implementation, when the plan uses it
+  bool stream_kernel;            // the persistent streaming kernel of nvfp4_stream.cu
+  bool overlap_launches;
+  nvfp4_stream::Config stream_config;
+  uint32_t* status;              // pinned; raised by a streaming launch whose bounded wait ran out
 };
 
 __global__ void __launch_bounds__(kThreads)
@@ -180,7 +185,34 @@ extern "C" int mircuda_fp4_vector_create(int n, int k, void* stream, void** outp
   // through global memory); measured on B200 it wins from about 24 MB of weights up (0.59 of
   // HBM speed against 0.48 at 24576 x 4096, 0.17 against 0.22 at 4096 x 4096).
   // MIRCUDA_B200_FP4_VECTOR=tensor or =simt overrides the choice.
+  // A third one, the persistent streaming kernel (nvfp4_stream.cu, shared with the bf16 x NVFP4
+  // op: the activation vector is dequantised into the warps' MMA fragments once per launch),
+  // beats both wherever it applies (whole 128-row scale tiles, K a multiple of 2048) and is the
+  // default there; =stream, =tensor or =simt in MIRCUDA_B200_FP4_VECTOR force a choice.
   const char* choice = std::getenv("MIRCUDA_B200_FP4_VECTOR");
+  const bool forced_other = choice != nullptr && (std::strcmp(choice, "tensor") == 0 || std::strcmp(choice, "simt") == 0);
+  if (!forced_other && mircuda_b200::nvfp4_stream::eligible(n, k)) {
+    int status = mircuda_b200::nvfp4_stream::prepare(&plan->stream_config, n, k);
+    if (status == 0) {
+      status = static_cast<int>(cudaHostAlloc(reinterpret_cast<void**>(&plan->status), sizeof(uint32_t),
+                                              cudaHostAllocMapped));
+      if (status != 0) {
+        delete plan;
+        return status;
+      }
+      *plan->status = 0u;
+      plan->stream_kernel = true;
+      // Overlapped launches (see mircuda_b200_nvfp4_vector_*): on unless the environment says 0.
+      const char* overlap = std::getenv("MIRCUDA_B200_OVERLAP_LAUNCHES");
+      plan->overlap_launches = overlap == nullptr || overlap[0] == '1';
+      *output = plan;
+      return 0;
+    }
+    if (status != -1) {
+      delete plan;
+      return status;
+    }
+  }
   bool tensor = static_cast<size_t>(n) * static_cast<size_t>(k) / 2u >= (size_t{24} << 20);
   if (choice != nullptr && std::strcmp(choice, "tensor") == 0) tensor = true;
   if (choice != nullptr && std::strcmp(choice, "simt") == 0) tensor = false;
@@ -233,6 +265,13 @@ extern "C" int mircuda_fp4_vector_execute(void* raw, void* stream, const void* i
         reinterpret_cast<uintptr_t>(weight_scales)) & 15u) != 0u) {
     return -1;
   }
+  if (plan->stream_kernel) {
+    if (*static_cast<volatile uint32_t*>(plan->status) != 0u) return -3;
+    if ((reinterpret_cast<uintptr_t>(input_scales) & 1u) != 0u) return -1;
+    return mircuda_b200::nvfp4_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input,
+                                              input_scales, weight, weight_scales, output, 1, plan->n, plan->k,
+                                              alpha, plan->status);
+  }
   if (plan->tensor != nullptr) {
     if ((reinterpret_cast<uintptr_t>(input_scales) & 15u) != 0u) return -1;
     return mircuda_b200::fp4_vector_tc::execute(plan->tensor, cuda_stream, input, input_scales, weight,
@@ -251,6 +290,7 @@ extern "C" void mircuda_fp4_vector_destroy(void* raw) {
   auto* plan = static_cast<mircuda_b200::fp4_vector::Plan*>(raw);
   if (plan == nullptr) return;
   mircuda_b200::fp4_vector_tc::destroy(plan->tensor);
+  if (plan->status != nullptr) cudaFreeHost(plan->status);
   if (plan->partials != nullptr) cudaFreeAsync(plan->partials, plan->stream);
   if (plan->counters != nullptr) cudaFreeAsync(plan->counters, plan->stream);
   delete plan;

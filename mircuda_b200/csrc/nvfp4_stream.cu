@@ -182,12 +182,16 @@ struct Ring {
   static constexpr int kSlots = kTiles * CPW;
 };
 
-template <int CPW>
+// FP4_INPUT: the activations are one NVFP4 vector (E2M1 codes + swizzled UE4M3 block scales, the
+// operands of mircuda_fp4_vector_*) instead of bf16 rows; code x scale is exact in f16, so the
+// fragments hold the dequantised vector and everything after them is unchanged.
+template <int CPW, bool FP4_INPUT>
 __global__ void __launch_bounds__(kThreads, 1)
 nvfp4_stream_kernel(const uint8_t* __restrict__ weight, const uint8_t* __restrict__ weight_scales,
-                    const __nv_bfloat16* __restrict__ input, __nv_bfloat16* __restrict__ output,
-                    int m, int n, int k, int tiles, int passes, float global_scale,
-                    uint32_t* __restrict__ status) {
+                    const void* __restrict__ input_pointer, const uint8_t* __restrict__ input_scales,
+                    __nv_bfloat16* __restrict__ output, int m, int n, int k, int tiles, int passes,
+                    float global_scale, uint32_t* __restrict__ status) {
+  const __nv_bfloat16* input = static_cast<const __nv_bfloat16*>(input_pointer);
   extern __shared__ __align__(16) uint8_t shared[];
   const uint32_t shared_base = ptx::smem_address(shared);
   uint64_t* sums_full = reinterpret_cast<uint64_t*>(shared + SharedLayout::kBarriers);   // [kSumBuffers]
@@ -345,7 +349,31 @@ nvfp4_stream_kernel(const uint8_t* __restrict__ weight, const uint8_t* __restric
 #pragma unroll
       for (int part = 0; part < CPW; ++part) {
         const int element = ((pass * CPW + part) * kStageChunks + warp) * 128 + quad * 32;
-        if (group < m) {
+        if (FP4_INPUT) {
+          if (group == 0) {
+            // 32 codes (16 bytes) and the two block scales of K blocks element / 16 and + 1: in the
+            // one-row swizzled layout block c sits at byte (c / 4) * 512 + c % 4.
+            const uint8_t* bytes = static_cast<const uint8_t*>(input_pointer);
+            const uint4 codes = __ldg(reinterpret_cast<const uint4*>(bytes + element / 2));
+            const int block = element / 16;
+            const uint32_t both = decode_scales(
+                __ldg(reinterpret_cast<const uint16_t*>(input_scales + (block >> 2) * 512 + (block & 3))));
+            const uint32_t multiplier[2] = {prmt(both, both, 0x1010u), prmt(both, both, 0x3232u)};
+            const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+#pragma unroll
+            for (int word = 0; word < 4; ++word) {
+              uint32_t values[4];
+              decode_e2m1x8(words[word], values);
+#pragma unroll
+              for (int item = 0; item < 4; ++item) {
+                b[part][word * 4 + item] = mul_f16x2(values[item], multiplier[word >> 1]);
+              }
+            }
+          } else {
+#pragma unroll
+            for (int item = 0; item < 16; ++item) b[part][item] = 0u;
+          }
+        } else if (group < m) {
           const uint4* source = reinterpret_cast<const uint4*>(input + static_cast<size_t>(group) * k + element);
 #pragma unroll
           for (int word = 0; word < 4; ++word) {
@@ -434,14 +462,14 @@ nvfp4_stream_kernel(const uint8_t* __restrict__ weight, const uint8_t* __restric
   if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
 }
 
-using Kernel = void (*)(const uint8_t*, const uint8_t*, const __nv_bfloat16*, __nv_bfloat16*, int, int, int,
-                        int, int, float, uint32_t*);
+using Kernel = void (*)(const uint8_t*, const uint8_t*, const void*, const uint8_t*, __nv_bfloat16*, int,
+                        int, int, int, int, float, uint32_t*);
 
-Kernel kernel_for(int chunks_per_warp) {
+Kernel kernel_for(int chunks_per_warp, bool fp4_input) {
   switch (chunks_per_warp) {
-    case 1: return nvfp4_stream_kernel<1>;
-    case 2: return nvfp4_stream_kernel<2>;
-    default: return nvfp4_stream_kernel<3>;
+    case 1: return fp4_input ? nvfp4_stream_kernel<1, true> : nvfp4_stream_kernel<1, false>;
+    case 2: return fp4_input ? nvfp4_stream_kernel<2, true> : nvfp4_stream_kernel<2, false>;
+    default: return fp4_input ? nvfp4_stream_kernel<3, true> : nvfp4_stream_kernel<3, false>;
   }
 }
 
@@ -472,9 +500,12 @@ bool eligible(int n, int k) {
 int prepare(Config* config, int n, int k) {
   if (!eligible(n, k)) return -1;
   split_k(k, &config->chunks_per_warp, &config->passes);
-  Kernel kernel = kernel_for(config->chunks_per_warp);
-  int status = static_cast<int>(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                     SharedLayout::kBytes));
+  int status = 0;
+  for (int fp4_input = 0; fp4_input < 2 && status == 0; ++fp4_input) {
+    status = static_cast<int>(cudaFuncSetAttribute(kernel_for(config->chunks_per_warp, fp4_input != 0),
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   SharedLayout::kBytes));
+  }
   if (status != 0) return status;
   int device = 0, sm_count = 0;
   status = static_cast<int>(cudaGetDevice(&device));
@@ -490,8 +521,8 @@ int prepare(Config* config, int n, int k) {
 }
 
 int launch(Config* config, cudaStream_t stream, bool overlap_launches, const void* input,
-           const void* weight, const void* weight_scales, void* output, int m, int n, int k,
-           float global_scale, uint32_t* status) {
+           const void* input_scales, const void* weight, const void* weight_scales, void* output, int m,
+           int n, int k, float global_scale, uint32_t* status) {
   cudaLaunchConfig_t launch_config = {};
   launch_config.gridDim = dim3(config->ctas, 1, 1);
   launch_config.blockDim = dim3(kThreads, 1, 1);
@@ -503,9 +534,10 @@ int launch(Config* config, cudaStream_t stream, bool overlap_launches, const voi
   launch_config.attrs = attributes;
   launch_config.numAttrs = overlap_launches ? 1 : 0;
   return static_cast<int>(cudaLaunchKernelEx(
-      &launch_config, kernel_for(config->chunks_per_warp), static_cast<const uint8_t*>(weight),
-      static_cast<const uint8_t*>(weight_scales), static_cast<const __nv_bfloat16*>(input),
-      static_cast<__nv_bfloat16*>(output), m, n, k, n / kTileRows, config->passes, global_scale, status));
+      &launch_config, kernel_for(config->chunks_per_warp, input_scales != nullptr),
+      static_cast<const uint8_t*>(weight), static_cast<const uint8_t*>(weight_scales), input,
+      static_cast<const uint8_t*>(input_scales), static_cast<__nv_bfloat16*>(output), m, n, k,
+      n / kTileRows, config->passes, global_scale, status));
 }
 
 }  // namespace nvfp4_stream

@@ -22,9 +22,11 @@ bool eligible(int n, int k);
 // the shape needs more running sums than the kernel keeps (the caller then uses another kernel).
 int prepare(Config* config, int n, int k);
 
+// `input_scales` null: `input` is bf16 [m, k]. Otherwise `input` is one NVFP4 vector (k / 2 code
+// bytes) with its swizzled block scales, and m must be 1.
 int launch(Config* config, cudaStream_t stream, bool overlap_launches, const void* input,
-           const void* weight, const void* weight_scales, void* output, int m, int n, int k,
-           float global_scale, uint32_t* status);
+           const void* input_scales, const void* weight, const void* weight_scales, void* output, int m,
+           int n, int k, float global_scale, uint32_t* status);
 
 }  // namespace nvfp4_stream
 }  // namespace mircuda_b200

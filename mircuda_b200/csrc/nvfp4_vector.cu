@@ -673,8 +673,8 @@ extern "C" int mircuda_b200_nvfp4_vector_execute(void* raw, void* stream, const 
   }
   if (plan->stream_kernel) {
     if ((reinterpret_cast<uintptr_t>(output) & 1u) != 0u) return -1;
-    return nvfp4_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input, weight,
-                                weight_scales, output, plan->m, plan->n, plan->k, global_scale,
+    return nvfp4_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input, nullptr,
+                                weight, weight_scales, output, plan->m, plan->n, plan->k, global_scale,
                                 plan->status);
   }
   if (plan->direct) {

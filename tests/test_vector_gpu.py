@@ -100,10 +100,11 @@ def run_fp4_vector(stream, x, xs, w, ws, n, k, alpha):
     return bf16_bits(out)
 
 
-@pytest.fixture(params=["tensor", "simt"])
+@pytest.fixture(params=["stream", "tensor", "simt"])
 def fp4_vector_kernel(request, monkeypatch):
-    """Both implementations behind mircuda_fp4_vector_*: the tcgen05 kernel (chosen for large
-    weights) and the CUDA-core kernel; the override is read when a plan is created."""
+    """The implementations behind mircuda_fp4_vector_*: the persistent streaming kernel (default
+    where n % 128 == 0 and k % 2048 == 0; other shapes fall to the two below), the tcgen05 kernel
+    (large weights) and the CUDA-core kernel; the override is read when a plan is created."""
     monkeypatch.setenv("MIRCUDA_B200_FP4_VECTOR", request.param)
     return request.param
 
@@ -120,7 +121,7 @@ def test_fp4_vector_golden(cuda_stream, fp4_vector_kernel):
 
 
 @pytest.mark.parametrize("n,k", [(4096, 4096), (200, 448), (129, 64), (2048, 2816), (24576, 4096),
-                                 (4096, 12288), (128, 192)])
+                                 (4096, 12288), (128, 192), (6144, 4096), (256, 2048), (1152, 6144)])
 def test_fp4_vector_random(cuda_stream, fp4_vector_kernel, n, k):
     x, xs = random_fp4(1, k, 11)
     w, ws = random_fp4(n, k, 12)
