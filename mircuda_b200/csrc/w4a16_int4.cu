@@ -21,11 +21,14 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 #include <new>
 
 #include "ptx.cuh"
 #include "ptx_pair.cuh"
 #include "tensor_map.hpp"
+#include "w4a16_stream.hpp"
 
 extern "C" int mircuda_dense_create(int input_type, int output_type, int m, int n, int k,
                                     void* stream, void** output);
@@ -350,6 +353,9 @@ struct Plan {
   CUtensorMap weight_map;
   void* dense;               // tensor-core path: dense f16 plan and the expanded weights
   __half* expanded;
+  bool stream_kernel;        // the persistent streaming kernel of w4a16_stream.cu
+  bool overlap_launches;
+  w4a16_stream::Config stream_config;
 };
 
 int parts_for(int n, int k, int slots, int max_parts) {
@@ -415,7 +421,25 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
                                             sizeof(uint32_t), cudaHostAllocMapped));
   }
   if (status == 0) *plan->status = 0u;
+  // Decode shapes the persistent streaming kernel covers (n % 16 == 0, k % 2048 == 0) run on it:
+  // K=4096 x N=14336 at M=1 took 16.5 us on the ring kernel below. MIRCUDA_B200_W4A16=ring keeps
+  // the ring kernel. Launches overlap as for mircuda_b200_nvfp4_vector_* (weights and scales are
+  // fetched while earlier work of the stream may still run; MIRCUDA_B200_OVERLAP_LAUNCHES=0
+  // serialises them).
   if (status == 0 && m <= kVectorTokens) {
+    const char* choice = std::getenv("MIRCUDA_B200_W4A16");
+    if (!(choice != nullptr && std::strcmp(choice, "ring") == 0)) {
+      const int prepared = mircuda_b200::w4a16_stream::prepare(&plan->stream_config, m, n, k);
+      if (prepared == 0) {
+        plan->stream_kernel = true;
+        const char* overlap = std::getenv("MIRCUDA_B200_OVERLAP_LAUNCHES");
+        plan->overlap_launches = overlap == nullptr || overlap[0] == '1';
+      } else if (prepared != -1) {
+        status = prepared;
+      }
+    }
+  }
+  if (status == 0 && m <= kVectorTokens && !plan->stream_kernel) {
     plan->token_groups = m <= 8 ? 1 : 2;
     if (plan->token_groups == 1) {
       status = static_cast<int>(cudaFuncSetAttribute(w4a16_vector_kernel<1>,
@@ -428,7 +452,7 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
                                                      SharedLayout<2>::kBytes));
       plan->parts = parts_for(n, k, sm_count, SharedLayout<2>::kMaxParts);
     }
-  } else if (status == 0) {
+  } else if (status == 0 && m > kVectorTokens) {
     status = mircuda_dense_create(0, 0, m, n, k, stream, &plan->dense);
     if (status == 0) {
       status = static_cast<int>(cudaMallocAsync(reinterpret_cast<void**>(&plan->expanded),
@@ -469,6 +493,11 @@ extern "C" int mircuda_b200_w4a16_execute(void* raw, void* stream, const void* i
         reinterpret_cast<uintptr_t>(output)) & 15u) != 0u ||
       (reinterpret_cast<uintptr_t>(scales) & 1u) != 0u) {
     return -1;
+  }
+  if (plan->stream_kernel) {
+    if ((reinterpret_cast<uintptr_t>(scales) & 3u) != 0u) return -1;
+    return mircuda_b200::w4a16_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input, weight,
+                                scales, output, plan->m, plan->n, plan->k, plan->status);
   }
   if (plan->dense != nullptr) {
     const size_t words = static_cast<size_t>(plan->n) * plan->k / 8u;

@@ -99,9 +99,19 @@ def assert_w4a16_matches_oracle(out, x, packed, scales, what):
     assert_close(out, torch.from_numpy(expected.astype(np.float32)), what)
 
 
+@pytest.fixture(params=["stream", "ring"])
+def w4a16_kernel(request, monkeypatch):
+    """Decode kernels behind mircuda_b200_w4a16_*: the persistent streaming kernel (n % 16 == 0,
+    k % 2048 == 0, m <= 16; other shapes fall to the ring kernel) and the TMA-ring kernel."""
+    monkeypatch.setenv("MIRCUDA_B200_W4A16", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("m,n,k", [(1, 512, 1024), (4, 1000, 512), (8, 200, 128), (16, 640, 2048),
-                                   (9, 4096, 4096), (256, 512, 1024), (40, 264, 384)])
-def test_w4a16_random(cuda_stream, m, n, k):
+                                   (9, 4096, 4096), (256, 512, 1024), (40, 264, 384),
+                                   (1, 4096, 4096), (3, 2384, 2048), (8, 160, 6144), (12, 1024, 6144),
+                                   (16, 48, 4096)])
+def test_w4a16_random(cuda_stream, w4a16_kernel, m, n, k):
     """Device quantiser (bit-exact against the oracle's) and the product against the oracle's
     (q - 8) * scale restatement, sys/native/marlin/vendor/dequant.h:107-216."""
     import oracle
@@ -119,7 +129,7 @@ def test_w4a16_random(cuda_stream, m, n, k):
 
 @pytest.mark.parametrize("m", [1, 16, 256])
 @pytest.mark.parametrize("n,k", [(14336, 4096), (4096, 14336)])
-def test_w4a16_benchmark_shapes(cuda_stream, m, n, k):
+def test_w4a16_benchmark_shapes(cuda_stream, w4a16_kernel, m, n, k):
     """The Marlin-style W4A16 shapes the throughput is quoted on: K=4096 x N=14336 and
     K=14336 x N=4096, weights ~N(0, 0.02) quantised by the oracle (symmetric zero point 8,
     group 128, f16 scales = max|w|/7), f16 activations ~N(0, 1) at M in {1, 16, 256}."""
