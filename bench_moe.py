@@ -167,6 +167,9 @@ def main() -> None:
                                      if gemm_ms else None),
             "stage_ms_rank0": {name: round(value, 4) for name, value in gemm_ms.items() if name not in flops},
             "cuda_graph": bool(args.graph),
+            # NVFP4: SwiGLU and the requantisation run inside the gate_up epilogue (its time then
+            # includes them and no separate stage exists)
+            "fused_gate_up_epilogue": bool(nvfp4 and layer.static_scales and bank.fused and layer.fuse_swiglu),
             "config": {"workload": "qwen3-30b-a3b moe feed-forward", "experts": EXPERTS, "top_k": TOP_K,
                        "hidden": HIDDEN, "intermediate": INTERMEDIATE, "tokens": TOKENS,
                        "capacity_rows": capacity,

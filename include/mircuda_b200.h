@@ -238,6 +238,20 @@ int mircuda_variable_grouped_fp4_execute(void* plan, void* stream, const void* a
                                          const unsigned int* offsets,
                                          const unsigned int* scale_offsets, void* c);
 void mircuda_variable_grouped_fp4_destroy(void* plan);
+/* NEW: the same product with the MoE activation fused into its epilogue. The plan's matrices are
+ * gate_up banks [2 I, k] whose rows interleave gate and up in runs of 16 (rows 32 b .. 32 b + 15 =
+ * gate rows 16 b .., rows 32 b + 16 .. 32 b + 31 = the up rows of the same columns; n = 2 I,
+ * n % 32 == 0). Instead of bf16 C it writes what the next grouped product reads: the E2M1 codes
+ * [capacity, I / 2] and swizzled UE4M3 scales (rows as in C) of bf16(silu(gate) * up) quantised
+ * with the device-resident tensor scale *global_scale; bit for bit the result of the plain
+ * execute on a [gate rows | up rows] bank followed by mircuda_b200_moe_swiglu_nvfp4. It removes
+ * one launch and the round trip of the [capacity, 2 I] bf16 intermediate through HBM (the
+ * fusion seam after the grouped plan of src/cutlass/variable_grouped/fp4/mod.rs:106-161). */
+int mircuda_b200_variable_grouped_fp4_execute_swiglu(
+    void* plan, void* stream, const void* a, const void* a_scales, const void* b,
+    const void* b_scales, const void* alphas, const unsigned int* indices, const unsigned int* rows,
+    const unsigned int* offsets, const unsigned int* scale_offsets, const void* global_scale,
+    void* codes, void* scales);
 /* Two such problems (left, right) that share indices / rows / offsets / scale_offsets. */
 int mircuda_paired_variable_grouped_fp4_create(int groups, int matrices, int max_m, int n, int k,
                                                void* stream, void** output);

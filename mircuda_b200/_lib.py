@@ -94,6 +94,7 @@ SIGNATURES.update({
     "mircuda_b200_moe_swiglu_nvfp4": (_i, [_vp, _vp, _vp, _vp, _u32, _vp, _u32, _vp]),
     "mircuda_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_variable_grouped_fp4_execute": (_i, [_vp] * 12),
+    "mircuda_b200_variable_grouped_fp4_execute_swiglu": (_i, [_vp] * 14),
     "mircuda_variable_grouped_fp4_destroy": (None, [_vp]),
     "mircuda_paired_variable_grouped_fp4_create": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_paired_variable_grouped_fp4_execute": (_i, [_vp] * 18),

@@ -28,6 +28,8 @@
 #include <cstdint>
 #include <new>
 
+#include "layout.cuh"
+#include "nvfp4_block.cuh"
 #include "ptx.cuh"
 #include "tensor_map.hpp"
 
@@ -87,6 +89,13 @@ struct Side {
   const uint8_t* b_scales;
   const float* alphas;
   __nv_bfloat16* c;
+  // Fused SwiGLU + NVFP4 requantisation (null `codes`: plain bf16 output). The matrices then
+  // hold gate and up rows interleaved in runs of 16 (rows 32 b .. 32 b + 15 = gate rows
+  // 16 b .. 16 b + 15, rows 32 b + 16 .. 32 b + 31 = the up rows of the same columns), so that
+  // one 32-column piece of an accumulator row is one 16-element block of the activation.
+  uint2* codes;               // [capacity, n / 4] bytes: E2M1 codes of silu(gate) * up
+  uint8_t* out_scales;        // swizzled UE4M3 scales of that tensor, rows as in C
+  const float* out_global;    // its tensor scale (device)
 };
 
 struct Sides {
@@ -424,7 +433,32 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
         ptx::tmem_load_32x32(tmem_row + chunk * 32u, values);
         ptx::tmem_load_wait();
         const uint32_t column = tile.n0 + chunk * 32u;
-        if (row_valid && column < n) {
+        if (side.codes != nullptr) {
+          // gate_up -> SwiGLU -> NVFP4: columns 0..15 of the piece are gate, 16..31 up, of output
+          // block column / 32; each value is rounded to bf16 first, as the unfused path stores it.
+          if (row_valid && column + 32u <= n) {
+            uint32_t gate[8], up[8];
+#pragma unroll
+            for (uint32_t pair = 0; pair < 8u; ++pair) {
+              const __nv_bfloat162 g = __floats2bfloat162_rn(__uint_as_float(values[2u * pair]) * alpha,
+                                                             __uint_as_float(values[2u * pair + 1u]) * alpha);
+              const __nv_bfloat162 u = __floats2bfloat162_rn(__uint_as_float(values[16u + 2u * pair]) * alpha,
+                                                             __uint_as_float(values[17u + 2u * pair]) * alpha);
+              gate[pair] = *reinterpret_cast<const uint32_t*>(&g);
+              up[pair] = *reinterpret_cast<const uint32_t*>(&u);
+            }
+            const uint4 first = nvfp4_block::swiglu8(make_uint4(gate[0], gate[1], gate[2], gate[3]),
+                                                     make_uint4(up[0], up[1], up[2], up[3]));
+            const uint4 second = nvfp4_block::swiglu8(make_uint4(gate[4], gate[5], gate[6], gate[7]),
+                                                      make_uint4(up[4], up[5], up[6], up[7]));
+            uint8_t scale_code = 0u;
+            const uint2 packed = nvfp4_block::quantize_block16(first, second, __ldg(side.out_global), &scale_code);
+            const uint32_t out_row = tile.group.c_row + tile.row_tile * kBlockM + row_in_tile;
+            const uint32_t blocks = n / 32u;
+            side.codes[static_cast<size_t>(out_row) * blocks + column / 32u] = packed;
+            side.out_scales[scale_offset(out_row, column / 32u, blocks)] = scale_code;
+          }
+        } else if (row_valid && column < n) {
           __nv_bfloat16* destination = c_row + column;
           if (vector_stores && column + 32u <= n) {
 #pragma unroll
@@ -569,7 +603,9 @@ struct Operands {
   const void* b;
   const void* b_scales;
   const void* alphas;
-  void* c;
+  void* c;                    // bf16 output, or the code bytes when `out_scales` is given
+  void* out_scales = nullptr;
+  const void* out_global = nullptr;
 };
 
 int bind_side(Plan* plan, int index, const Operands& operands) {
@@ -602,7 +638,18 @@ int bind_side(Plan* plan, int index, const Operands& operands) {
   side.a_scales = static_cast<const uint8_t*>(operands.a_scales);
   side.b_scales = static_cast<const uint8_t*>(operands.b_scales);
   side.alphas = static_cast<const float*>(operands.alphas);
-  side.c = static_cast<__nv_bfloat16*>(operands.c);
+  if (operands.out_scales != nullptr) {
+    if (operands.out_global == nullptr || plan->n % 32 != 0) return -1;
+    side.c = nullptr;
+    side.codes = static_cast<uint2*>(operands.c);
+    side.out_scales = static_cast<uint8_t*>(operands.out_scales);
+    side.out_global = static_cast<const float*>(operands.out_global);
+  } else {
+    side.c = static_cast<__nv_bfloat16*>(operands.c);
+    side.codes = nullptr;
+    side.out_scales = nullptr;
+    side.out_global = nullptr;
+  }
   return 0;
 }
 
@@ -658,6 +705,23 @@ extern "C" int mircuda_variable_grouped_fp4_execute(
   Plan* plan = nullptr;
   int status = check(raw, stream, Mode::kVariable, &plan);
   if (status == 0) status = bind_side(plan, 0, Operands{a, a_scales, b, b_scales, alphas, c});
+  if (status == 0) status = setup_variable(plan, indices, rows, offsets, scale_offsets);
+  if (status == 0) status = run(plan, 1u);
+  return status;
+}
+
+extern "C" int mircuda_b200_variable_grouped_fp4_execute_swiglu(
+    void* raw, void* stream, const void* a, const void* a_scales, const void* b,
+    const void* b_scales, const void* alphas, const unsigned int* indices,
+    const unsigned int* rows, const unsigned int* offsets, const unsigned int* scale_offsets,
+    const void* global_scale, void* codes, void* scales) {
+  using namespace mircuda_b200::grouped_fp4;
+  Plan* plan = nullptr;
+  int status = check(raw, stream, Mode::kVariable, &plan);
+  if (status == 0 && (global_scale == nullptr || scales == nullptr)) status = -1;
+  if (status == 0) {
+    status = bind_side(plan, 0, Operands{a, a_scales, b, b_scales, alphas, codes, scales, global_scale});
+  }
   if (status == 0) status = setup_variable(plan, indices, rows, offsets, scale_offsets);
   if (status == 0) status = run(plan, 1u);
   return status;

@@ -95,9 +95,14 @@ class ExpertWeights:
     """The rank's expert banks: gate_up [local_experts, 2*intermediate, hidden] and
     down [local_experts, hidden, intermediate] in bf16, quantised to NVFP4 on request."""
 
-    def __init__(self, stream, gate_up: torch.Tensor, down: torch.Tensor, nvfp4: bool):
+    def __init__(self, stream, gate_up: torch.Tensor, down: torch.Tensor, nvfp4: bool,
+                 fuse_swiglu: bool = True):
+        """`fuse_swiglu` (NVFP4 only): also keep a gate_up bank whose rows interleave gate and up
+        in runs of 16, the layout `mircuda_b200_variable_grouped_fp4_execute_swiglu` reads; the
+        layer then runs SwiGLU and the requantisation inside the gate_up epilogue."""
         self.gate_up, self.down = gate_up.contiguous(), down.contiguous()
         self.nvfp4 = nvfp4
+        self.fused = False
         if nvfp4:
             # One quantiser pass per bank: every matrix has a whole number of 128-row scale
             # tiles, so the bank's scale layout is the concatenation of the matrices' layouts.
@@ -109,6 +114,18 @@ class ExpertWeights:
                 setattr(self, f"{name}_codes", codes.reshape(-1))
                 setattr(self, f"{name}_scales", scales)
                 setattr(self, f"{name}_global", global_scale)
+            local_experts, two_i, k = self.gate_up.shape
+            intermediate = two_i // 2
+            if fuse_swiglu and intermediate % 16 == 0:
+                # rows [gate 16 b .. | up 16 b ..] per block b; quantisation is per row, so the
+                # bank's codes and scales are those of the plain bank, permuted
+                gate = self.gate_up[:, :intermediate].reshape(local_experts, intermediate // 16, 16, k)
+                up = self.gate_up[:, intermediate:].reshape(local_experts, intermediate // 16, 16, k)
+                interleaved = torch.cat([gate, up], dim=2).reshape(local_experts * two_i, k).contiguous()
+                codes, scales, global_scale = plans.nvfp4_quantize_bf16(stream, interleaved)
+                self.gate_up_fused_codes, self.gate_up_fused_scales = codes.reshape(-1), scales
+                self.gate_up_fused_global = global_scale
+                self.fused = True
 
 
 class ExpertParallelMoe:
@@ -238,6 +255,7 @@ class ExpertParallelMoe:
                 groups, capacity, hidden, intermediate, rows, self.local_experts))
         self.gemm_events = None   # set to a list to record (name, start, stop) CUDA events
         self.static_scales = False
+        self.fuse_swiglu = True   # use the fused gate_up epilogue once the scales are frozen
         # Raised by the layout kernel when the routing sends an owner more rows than its buffers
         # hold. Pinned host memory: kernels write it through its device-visible address and the
         # host reads it without touching the stream.
@@ -410,10 +428,20 @@ class ExpertParallelMoe:
             self._timed("scale atoms", lambda: plans._check(lib.mircuda_b200_moe_scale_atoms(
                 self._p(self.received_scales), self._p(self.scales1), rows, self._p(self.received_rows),
                 self.hidden // 16, handle)))
-            self._timed("gate_up", lambda: self.plan1.execute(
-                self.received_codes, self.scales1, w.gate_up_codes, w.gate_up_scales, self.alphas1,
-                self.indices, self.rows, self.offsets, self.offsets, self.hidden_states))
-            if self.static_scales:
+            if self.static_scales and w.fused and self.fuse_swiglu:
+                # gate_up with SwiGLU and the requantisation in its epilogue: the bf16 intermediate
+                # never exists
+                self._timed("gate_up", lambda: self.plan1.execute_swiglu(
+                    self.received_codes, self.scales1, w.gate_up_fused_codes, w.gate_up_fused_scales,
+                    self.alphas1, self.indices, self.rows, self.offsets, self.offsets, self.global2,
+                    self.codes2, self.scales2))
+            else:
+                self._timed("gate_up", lambda: self.plan1.execute(
+                    self.received_codes, self.scales1, w.gate_up_codes, w.gate_up_scales, self.alphas1,
+                    self.indices, self.rows, self.offsets, self.offsets, self.hidden_states))
+            if self.static_scales and w.fused and self.fuse_swiglu:
+                pass
+            elif self.static_scales:
                 self._timed("swiglu + quantize", lambda: plans._check(lib.mircuda_b200_moe_swiglu_nvfp4(
                     self._p(self.hidden_states), self._p(self.global2), self._p(self.codes2),
                     self._p(self.scales2), rows, self._p(self.received_rows), self.intermediate, handle)))
@@ -507,6 +535,14 @@ class _RawGroupedFp4:
         plans._check(self._lib.mircuda_variable_grouped_fp4_execute(
             self._raw, ctypes.c_void_p(self._stream.cuda_stream), p(a), p(a_scales), p(b), p(b_scales),
             p(alphas), p(indices), p(rows), p(offsets), p(scale_offsets), p(c)))
+
+    def execute_swiglu(self, a, a_scales, b, b_scales, alphas, indices, rows, offsets, scale_offsets,
+                       global_scale, codes, scales):
+        p = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+        plans._check(self._lib.mircuda_b200_variable_grouped_fp4_execute_swiglu(
+            self._raw, ctypes.c_void_p(self._stream.cuda_stream), p(a), p(a_scales), p(b), p(b_scales),
+            p(alphas), p(indices), p(rows), p(offsets), p(scale_offsets), p(global_scale), p(codes),
+            p(scales)))
 
     def close(self):
         if getattr(self, "_raw", None):

@@ -357,3 +357,92 @@ def test_layer_reports_an_exceeded_capacity(cuda_stream):
         layer.check()
     assert torch.isfinite(out.float()).all()
     layer.close()
+
+
+def test_gate_up_epilogue_fusion_matches_two_passes(cuda_stream):
+    """gate_up with SwiGLU and the NVFP4 requantisation in its epilogue (gate and up rows of the
+    bank interleaved in runs of 16) against the plain grouped product on the [gate | up] bank
+    followed by the fused SwiGLU quantiser: same codes and scales, bit for bit, for every row a
+    group owns; rows no group owns are left alone."""
+    import ctypes
+    from mircuda_b200 import _lib, plans, plans_fp4
+    library = _lib.load()
+    experts, intermediate, hidden = 5, 192, 256
+    rows = [130, 0, 77, 128, 1]
+    offsets = [0, 256, 256, 384, 512]                 # every group starts on a 128-row tile
+    capacity = 640
+    generator = torch.Generator(device="cuda").manual_seed(321)
+    bank = (torch.randn(experts, 2 * intermediate, hidden, generator=generator, device="cuda") * 0.05).to(torch.bfloat16)
+    gate = bank[:, :intermediate].reshape(experts, intermediate // 16, 16, hidden)
+    up = bank[:, intermediate:].reshape(experts, intermediate // 16, 16, hidden)
+    interleaved = torch.cat([gate, up], dim=2).reshape(experts * 2 * intermediate, hidden).contiguous()
+    x = torch.randn(capacity, hidden, generator=generator, device="cuda").to(torch.bfloat16)
+    torch.cuda.synchronize()
+    a_codes, a_scales, a_global = plans.nvfp4_quantize_bf16(cuda_stream, x)
+    plain_codes, plain_scales, bank_global = plans.nvfp4_quantize_bf16(cuda_stream, bank.view(-1, hidden))
+    fused_codes, fused_scales, fused_global = plans.nvfp4_quantize_bf16(cuda_stream, interleaved)
+    cuda_stream.synchronize()
+    assert float(bank_global) == float(fused_global)
+    alphas = (bank_global * a_global).expand(experts).contiguous()
+    words = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    indices, rows_d, offsets_d = words(list(range(experts))), words(rows), words(offsets)
+    p = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    handle = ctypes.c_void_p(cuda_stream.cuda_stream)
+    raw = ctypes.c_void_p()
+    assert library.mircuda_variable_grouped_fp4_create(experts, experts, capacity, 2 * intermediate, hidden,
+                                                       handle, ctypes.byref(raw)) == 0
+    hidden_states = torch.zeros(capacity, 2 * intermediate, dtype=torch.bfloat16, device="cuda")
+    out_global = torch.full((1,), 0.0042, dtype=torch.float32, device="cuda")
+    scale_bytes = capacity // 128 * (intermediate // 64) * 512
+    expected_codes = torch.zeros(capacity * intermediate // 2, dtype=torch.uint8, device="cuda")
+    expected_scales = torch.zeros(scale_bytes, dtype=torch.uint8, device="cuda")
+    actual_codes = torch.full((capacity * intermediate // 2,), 0xEE, dtype=torch.uint8, device="cuda")
+    actual_scales = torch.full((scale_bytes,), 0xEE, dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    assert library.mircuda_variable_grouped_fp4_execute(
+        raw, handle, p(a_codes), p(a_scales), p(plain_codes), p(plain_scales), p(alphas), p(indices),
+        p(rows_d), p(offsets_d), p(offsets_d), p(hidden_states)) == 0
+    assert library.mircuda_b200_moe_swiglu_nvfp4(p(hidden_states), p(out_global), p(expected_codes),
+                                                 p(expected_scales), capacity, None, intermediate, handle) == 0
+    for _ in range(2):
+        assert library.mircuda_b200_variable_grouped_fp4_execute_swiglu(
+            raw, handle, p(a_codes), p(a_scales), p(fused_codes), p(fused_scales), p(alphas), p(indices),
+            p(rows_d), p(offsets_d), p(offsets_d), p(out_global), p(actual_codes), p(actual_scales)) == 0
+    cuda_stream.synchronize()
+    library.mircuda_variable_grouped_fp4_destroy(raw)
+    import oracle
+    owned = np.zeros(capacity, bool)
+    for count, first in zip(rows, offsets):
+        owned[first:first + count] = True
+    expected = expected_codes.cpu().numpy().reshape(capacity, intermediate // 2)
+    actual = actual_codes.cpu().numpy().reshape(capacity, intermediate // 2)
+    assert np.array_equal(actual[owned], expected[owned])
+    assert (actual[~owned] == 0xEE).all()
+    assert actual[owned].any()
+    positions = oracle.fp4_scale_offsets(capacity, intermediate)          # [capacity, intermediate / 16]
+    expected_bytes, actual_bytes = expected_scales.cpu().numpy(), actual_scales.cpu().numpy()
+    assert np.array_equal(actual_bytes[positions[owned]], expected_bytes[positions[owned]])
+    assert (actual_bytes[positions[~owned]] == 0xEE).all()
+
+
+def test_layer_with_and_without_epilogue_fusion(cuda_stream):
+    """The NVFP4 layer gives the same output, bit for bit, with the fused gate_up epilogue and
+    with the separate SwiGLU quantiser."""
+    from mircuda_b200 import moe
+    device = torch.device("cuda", torch.cuda.current_device())
+    x, gate_up, down, logits = make_inputs(device)
+    chosen, weights = moe.route(logits, TOP_K)
+    dispatch = moe.plan_dispatch(chosen, EXPERTS, 1, None, 128)
+    capacity = (TOKENS * TOP_K + 128 * EXPERTS) // 128 * 128
+    bank = moe.ExpertWeights(cuda_stream, gate_up, down, True)
+    assert bank.fused
+    layer = moe.ExpertParallelMoe(cuda_stream, HIDDEN, INTERMEDIATE, EXPERTS, TOP_K, TOKENS, capacity, bank)
+    layer.calibrate(x, dispatch, weights)
+    torch.cuda.synchronize()
+    outputs = []
+    for fuse in (True, False):
+        layer.fuse_swiglu = fuse
+        outputs.append(layer.forward(x, dispatch, weights).clone())
+        cuda_stream.synchronize()
+    assert torch.equal(outputs[0], outputs[1])
+    layer.close()
