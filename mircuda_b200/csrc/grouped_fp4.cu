@@ -26,6 +26,7 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdlib>
 #include <new>
 
 #include "layout.cuh"
@@ -37,7 +38,6 @@ namespace mircuda_b200 {
 namespace grouped_fp4 {
 
 constexpr uint32_t kBlockM = 128;
-constexpr uint32_t kBlockN = 128;
 constexpr uint32_t kStageBytesK = 128;     // 256 E2M1 codes per stage row
 constexpr uint32_t kStageElements = 256;
 constexpr uint32_t kAtomBytes = 512;
@@ -45,17 +45,24 @@ constexpr uint32_t kAtomsK = 4;            // scale atoms (64 K-elements each) p
 constexpr uint32_t kThreads = 192;
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kPieceMaps = 8;         // A tensor maps with box rows 128, 64, ..., 1
-constexpr uint32_t kStages = 6;
-constexpr uint32_t kAccStages = 2;
 
+// Tile width BN: 128 (two accumulators in tensor memory, six stages; the default) or 256 (one
+// accumulator, four stages). The wide tile reads every A tile half as often and halves the
+// tile count, but its single accumulator makes the MMAs of the next tile wait for the epilogue.
+template <uint32_t BN>
 struct Layout {
+  static_assert(BN == 128 || BN == 256, "supported tile widths");
+  static constexpr uint32_t kStages = BN == 128 ? 6 : 4;
+  static constexpr uint32_t kAccStages = BN == 128 ? 2 : 1;
+  static constexpr uint32_t kAtomsN = BN / 128;                      // 128-row scale tiles of B per tile
   static constexpr uint32_t kABytes = kBlockM * kStageBytesK;
-  static constexpr uint32_t kBBytes = kBlockN * kStageBytesK;
-  static constexpr uint32_t kSfBytes = kAtomsK * kAtomBytes;         // per operand and stage
+  static constexpr uint32_t kBBytes = BN * kStageBytesK;
+  static constexpr uint32_t kSfaBytes = kAtomsK * kAtomBytes;        // per stage
+  static constexpr uint32_t kSfbBytes = kAtomsN * kAtomsK * kAtomBytes;
   static constexpr uint32_t kBOffset = kStages * kABytes;
   static constexpr uint32_t kSfaOffset = kBOffset + kStages * kBBytes;
-  static constexpr uint32_t kSfbOffset = kSfaOffset + kStages * kSfBytes;
-  static constexpr uint32_t kBarrierOffset = kSfbOffset + kStages * kSfBytes;
+  static constexpr uint32_t kSfbOffset = kSfaOffset + kStages * kSfaBytes;
+  static constexpr uint32_t kBarrierOffset = kSfbOffset + kStages * kSfbBytes;
   static constexpr uint32_t kBarriers = 2 * kStages + 2 * kAccStages;
   static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
   // Tile starts of up to kSharedGroups groups, copied once per CTA: the per-tile binary search
@@ -64,9 +71,10 @@ struct Layout {
   static constexpr uint32_t kSharedGroups = 1024;
   static constexpr uint32_t kStartsOffset = kMiscOffset + 16;
   static constexpr uint32_t kDynamicBytes = kStartsOffset + (kSharedGroups + 1) * 4 + 1024;
-  // Tensor memory: two accumulators, then per stage 16 columns of A scales + 16 of B scales.
-  static constexpr uint32_t kSfColumn = kAccStages * kBlockN;
-  static constexpr uint32_t kSfColumnsPerStage = 8 * kAtomsK;
+  // Tensor memory: the accumulators, then per stage 16 columns of A scales and 16 per 128 rows
+  // of B scales ([K atom][128-row tile of B][4 columns], the order the MMA reads them in).
+  static constexpr uint32_t kSfColumn = kAccStages * BN;
+  static constexpr uint32_t kSfColumnsPerStage = 4 * kAtomsK * (1 + kAtomsN);
   static_assert(kSfColumn + kStages * kSfColumnsPerStage <= kTmemColumns, "tensor memory budget");
   static_assert(kDynamicBytes <= 232448, "shared memory budget");
 };
@@ -194,7 +202,8 @@ struct Tile {
 
 // Linear tile index (within one side) -> tile. Inside a group, row tiles vary fastest.
 __device__ __forceinline__ Tile locate(uint32_t index, const Group* __restrict__ records,
-                                       uint32_t groups, const uint32_t* shared_starts) {
+                                       uint32_t groups, const uint32_t* shared_starts,
+                                       uint32_t block_n) {
   uint32_t low = 0u, high = groups;       // last group whose start is <= index
   if (shared_starts != nullptr) {
     while (high - low > 1u) {
@@ -223,15 +232,18 @@ __device__ __forceinline__ Tile locate(uint32_t index, const Group* __restrict__
   const uint32_t local = index - tile.group.tile_start;
   tile.row_tile = local % row_tiles;
   tile.valid_rows = min(kBlockM, tile.group.rows - tile.row_tile * kBlockM);
-  tile.n0 = (local / row_tiles) * kBlockN;
+  tile.n0 = (local / row_tiles) * block_n;
   return tile;
 }
 
+template <uint32_t BN>
 __global__ void __launch_bounds__(kThreads, 1)
 grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
                    const Group* __restrict__ records, const uint32_t* __restrict__ total_tiles,
                    uint32_t groups, uint32_t n, uint32_t k, uint32_t* __restrict__ status) {
-  using L = Layout;
+  using L = Layout<BN>;
+  constexpr uint32_t kStages = L::kStages;
+  constexpr uint32_t kAccStages = L::kAccStages;
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t misalignment = ptx::smem_address(dynamic_shared) & 1023u;
   uint8_t* shared = dynamic_shared + ((1024u - misalignment) & 1023u);
@@ -295,7 +307,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
       Tile upcoming = {};
       if (blockIdx.x < tiles) {
         upcoming = locate(blockIdx.x >= side_tiles ? blockIdx.x - side_tiles : blockIdx.x, records,
-                          groups, shared_starts);
+                          groups, shared_starts, BN);
       }
       for (uint32_t index = blockIdx.x; running && index < tiles; index += gridDim.x) {
         const Side& side = sides.side[index >= side_tiles ? 1 : 0];
@@ -303,7 +315,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
         const uint32_t following = index + gridDim.x;
         if (following < tiles) {
           upcoming = locate(following >= side_tiles ? following - side_tiles : following, records,
-                            groups, shared_starts);
+                            groups, shared_starts, BN);
         }
         const uint32_t a_row = tile.group.a_row + tile.row_tile * kBlockM;
         const uint8_t* a_scales =
@@ -319,7 +331,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
           const uint32_t atoms_here = min(kAtomsK, atoms_k - ks * kAtomsK);
           ptx::mbarrier_arrive_expect_tx(
               &full[stage],
-              tile.valid_rows * kStageBytesK + L::kBBytes + 2u * atoms_here * kAtomBytes);
+              tile.valid_rows * kStageBytesK + L::kBBytes + (1u + L::kAtomsN) * atoms_here * kAtomBytes);
           uint8_t* a_stage = shared_a + stage * L::kABytes;
           const int32_t x = static_cast<int32_t>(ks * kStageBytesK);
           if (tile.valid_rows == kBlockM) {
@@ -341,12 +353,15 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
           }
           ptx::tma_load_3d(shared_b + stage * L::kBBytes, &side.b, &full[stage], x,
                            static_cast<int32_t>(tile.n0), static_cast<int32_t>(tile.group.matrix));
-          ptx::bulk_load(shared_sfa + stage * L::kSfBytes,
+          ptx::bulk_load(shared_sfa + stage * L::kSfaBytes,
                          a_scales + static_cast<size_t>(ks) * kAtomsK * kAtomBytes,
                          atoms_here * kAtomBytes, &full[stage]);
-          ptx::bulk_load(shared_sfb + stage * L::kSfBytes,
-                         b_scales + static_cast<size_t>(ks) * kAtomsK * kAtomBytes,
-                         atoms_here * kAtomBytes, &full[stage]);
+#pragma unroll
+          for (uint32_t tile_n = 0; tile_n < L::kAtomsN; ++tile_n) {     // 128-row scale tiles of B
+            ptx::bulk_load(shared_sfb + stage * L::kSfbBytes + tile_n * kAtomsK * kAtomBytes,
+                           b_scales + (static_cast<size_t>(tile_n) * atoms_k + static_cast<size_t>(ks) * kAtomsK) * kAtomBytes,
+                           atoms_here * kAtomBytes, &full[stage]);
+          }
           if (++stage == kStages) {
             stage = 0;
             phase ^= 1u;
@@ -361,13 +376,13 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
     // -------------------------------------------------------------------- MMA issuer
     if (ptx::elect_one()) {
       constexpr uint32_t idesc = ptx::make_block_scaled_idesc(
-          ptx::kFormatE2M1_mxf4, ptx::kFormatE2M1_mxf4, kBlockM, kBlockN, false);
+          ptx::kFormatE2M1_mxf4, ptx::kFormatE2M1_mxf4, kBlockM, BN, false);
       uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
       bool running = true;
       for (uint32_t index = blockIdx.x; running && index < tiles; index += gridDim.x) {
         if (!ptx::mbarrier_wait(&acc_empty[acc_stage], acc_phase ^ 1u, abort)) break;
         ptx::tcgen05_fence_after();
-        const uint32_t d_tmem = tmem_base + acc_stage * kBlockN;
+        const uint32_t d_tmem = tmem_base + acc_stage * BN;
         for (uint32_t ks = 0; ks < k_stages; ++ks) {
           if (!ptx::mbarrier_wait(&full[stage], phase, abort)) {
             running = false;
@@ -381,11 +396,14 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
             ptx::tcgen05_copy_scales(
                 sfa_tmem + 4u * atom,
                 ptx::make_scale_descriptor(
-                    ptx::smem_address(shared_sfa + stage * L::kSfBytes + atom * kAtomBytes)));
-            ptx::tcgen05_copy_scales(
-                sfb_tmem + 4u * atom,
-                ptx::make_scale_descriptor(
-                    ptx::smem_address(shared_sfb + stage * L::kSfBytes + atom * kAtomBytes)));
+                    ptx::smem_address(shared_sfa + stage * L::kSfaBytes + atom * kAtomBytes)));
+#pragma unroll
+            for (uint32_t tile_n = 0; tile_n < L::kAtomsN; ++tile_n) {
+              ptx::tcgen05_copy_scales(
+                  sfb_tmem + 4u * (atom * L::kAtomsN + tile_n),
+                  ptx::make_scale_descriptor(ptx::smem_address(
+                      shared_sfb + stage * L::kSfbBytes + (tile_n * kAtomsK + atom) * kAtomBytes)));
+            }
           }
           const uint64_t a_descriptor =
               ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_a + stage * L::kABytes));
@@ -394,7 +412,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
           for (uint32_t kb = 0; kb < atoms_here; ++kb) {
             // 32 bytes (64 codes) further along K inside the 128-byte swizzle span.
             ptx::mma_nvf4_block16(d_tmem, a_descriptor + 2u * kb, b_descriptor + 2u * kb, idesc,
-                                  sfa_tmem + 4u * kb, sfb_tmem + 4u * kb, (ks | kb) != 0u);
+                                  sfa_tmem + 4u * kb, sfb_tmem + 4u * kb * L::kAtomsN, (ks | kb) != 0u);
           }
           ptx::tcgen05_commit(&empty[stage]);
           if (++stage == kStages) {
@@ -415,23 +433,32 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
     const uint32_t quarter = warp % 4u;
     const bool vector_stores = (n % 8u) == 0u;
     uint32_t acc_stage = 0, acc_phase = 0;
+    // 32-byte stores need rows that start on 32-byte boundaries (n % 16 == 0 and such a base)
+    const bool wide_stores = (n % 16u) == 0u &&
+                             ((reinterpret_cast<uintptr_t>(sides.side[0].c) | reinterpret_cast<uintptr_t>(sides.side[1].c)) & 31u) == 0u;
+    // The next tile's record and alpha are fetched while this tile is drained (two dependent
+    // global loads after a search: about a microsecond if taken when the tile is due).
+    Tile upcoming = {};
+    float upcoming_alpha = 0.0f;
+    if (blockIdx.x < tiles) {
+      upcoming = locate(blockIdx.x >= side_tiles ? blockIdx.x - side_tiles : blockIdx.x, records, groups,
+                        shared_starts, BN);
+      upcoming_alpha = __ldg(sides.side[blockIdx.x >= side_tiles ? 1 : 0].alphas + upcoming.group.matrix);
+    }
     for (uint32_t index = blockIdx.x; index < tiles; index += gridDim.x) {
       const Side& side = sides.side[index >= side_tiles ? 1 : 0];
-      const Tile tile = locate(index >= side_tiles ? index - side_tiles : index, records, groups,
-                               shared_starts);
-      const float alpha = __ldg(side.alphas + tile.group.matrix);
+      const Tile tile = upcoming;
+      const float alpha = upcoming_alpha;
       if (!ptx::mbarrier_wait(&acc_full[acc_stage], acc_phase, abort)) break;
       ptx::tcgen05_fence_after();
       const uint32_t row_in_tile = quarter * 32u + lane;
-      const uint32_t tmem_row = tmem_base + ((quarter * 32u) << 16) + acc_stage * kBlockN;
+      const uint32_t tmem_row = tmem_base + ((quarter * 32u) << 16) + acc_stage * BN;
       const bool row_valid = row_in_tile < tile.valid_rows;
-      __nv_bfloat16* c_row =
-          side.c + static_cast<size_t>(tile.group.c_row + tile.row_tile * kBlockM + row_in_tile) * n;
-#pragma unroll 1
-      for (uint32_t chunk = 0; chunk < kBlockN / 32u; ++chunk) {
-        uint32_t values[32];
-        ptx::tmem_load_32x32(tmem_row + chunk * 32u, values);
-        ptx::tmem_load_wait();
+      const uint32_t out_row = tile.group.c_row + tile.row_tile * kBlockM + row_in_tile;
+      __nv_bfloat16* c_row = side.c + static_cast<size_t>(out_row) * n;
+
+      // One 32-column piece of this thread's accumulator row.
+      auto write_piece = [&](const uint32_t (&values)[32], uint32_t chunk) {
         const uint32_t column = tile.n0 + chunk * 32u;
         if (side.codes != nullptr) {
           // gate_up -> SwiGLU -> NVFP4: columns 0..15 of the piece are gate, 16..31 up, of output
@@ -453,7 +480,6 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
                                                       make_uint4(up[4], up[5], up[6], up[7]));
             uint8_t scale_code = 0u;
             const uint2 packed = nvfp4_block::quantize_block16(first, second, __ldg(side.out_global), &scale_code);
-            const uint32_t out_row = tile.group.c_row + tile.row_tile * kBlockM + row_in_tile;
             const uint32_t blocks = n / 32u;
             side.codes[static_cast<size_t>(out_row) * blocks + column / 32u] = packed;
             side.out_scales[scale_offset(out_row, column / 32u, blocks)] = scale_code;
@@ -461,18 +487,31 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
         } else if (row_valid && column < n) {
           __nv_bfloat16* destination = c_row + column;
           if (vector_stores && column + 32u <= n) {
+            uint32_t packed[16];
 #pragma unroll
-            for (uint32_t part = 0; part < 4u; ++part) {
-              uint32_t packed[4];
+            for (uint32_t pair = 0; pair < 16u; ++pair) {
+              const __nv_bfloat162 two = __floats2bfloat162_rn(__uint_as_float(values[pair * 2u]) * alpha,
+                                                             __uint_as_float(values[pair * 2u + 1u]) * alpha);
+              packed[pair] = *reinterpret_cast<const uint32_t*>(&two);
+            }
+            if (wide_stores) {
+              // 32 bytes per store: every store fills whole 32-byte sectors. With 16-byte stores
+              // the same rows cost twice the L1 -> L2 write traffic (measured: 265 MB for a 134 MB
+              // output), which this kernel's L2-bound launches cannot spare.
 #pragma unroll
-              for (uint32_t pair = 0; pair < 4u; ++pair) {
-                const __nv_bfloat162 two = __floats2bfloat162_rn(
-                    __uint_as_float(values[part * 8u + pair * 2u]) * alpha,
-                    __uint_as_float(values[part * 8u + pair * 2u + 1u]) * alpha);
-                packed[pair] = *reinterpret_cast<const uint32_t*>(&two);
+              for (uint32_t half = 0; half < 2u; ++half) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(destination + half * 16u),
+                             "r"(packed[half * 8u + 0u]), "r"(packed[half * 8u + 1u]), "r"(packed[half * 8u + 2u]),
+                             "r"(packed[half * 8u + 3u]), "r"(packed[half * 8u + 4u]), "r"(packed[half * 8u + 5u]),
+                             "r"(packed[half * 8u + 6u]), "r"(packed[half * 8u + 7u])
+                             : "memory");
               }
-              reinterpret_cast<uint4*>(destination)[part] =
-                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            } else {
+#pragma unroll
+              for (uint32_t part = 0; part < 4u; ++part) {
+                reinterpret_cast<uint4*>(destination)[part] =
+                    make_uint4(packed[part * 4u], packed[part * 4u + 1u], packed[part * 4u + 2u], packed[part * 4u + 3u]);
+              }
             }
           } else {
 #pragma unroll
@@ -483,10 +522,39 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
             }
           }
         }
+      };
+
+      // Pieces alternate between two register buffers: the tensor-memory load of the next piece
+      // is in flight while this one is converted and stored. The accumulator goes back to the
+      // MMA warp as soon as its last piece has been read.
+      constexpr uint32_t kPieces = BN / 32u;
+      uint32_t even[32], odd[32];
+      ptx::tmem_load_32x32(tmem_row, even);
+      ptx::tmem_load_wait();
+#pragma unroll 1
+      for (uint32_t chunk = 0; chunk < kPieces; chunk += 2u) {
+        ptx::tmem_load_32x32(tmem_row + (chunk + 1u) * 32u, odd);
+        if (chunk == 0u) {
+          // first use of the wait: fetch the next tile's record behind the loads already issued
+          const uint32_t following = index + gridDim.x;
+          if (following < tiles) {
+            upcoming = locate(following >= side_tiles ? following - side_tiles : following, records, groups,
+                              shared_starts, BN);
+            upcoming_alpha = __ldg(sides.side[following >= side_tiles ? 1 : 0].alphas + upcoming.group.matrix);
+          }
+        }
+        write_piece(even, chunk);
+        ptx::tmem_load_wait();
+        if (chunk + 2u < kPieces) {
+          ptx::tmem_load_32x32(tmem_row + (chunk + 2u) * 32u, even);
+        } else {
+          ptx::tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) ptx::mbarrier_arrive(&acc_empty[acc_stage]);
+        }
+        write_piece(odd, chunk + 1u);
+        ptx::tmem_load_wait();
       }
-      ptx::tcgen05_fence_before();
-      __syncwarp();
-      if (lane == 0) ptx::mbarrier_arrive(&acc_empty[acc_stage]);
       if (++acc_stage == kAccStages) {
         acc_stage = 0;
         acc_phase ^= 1u;
@@ -519,16 +587,17 @@ struct Plan {
   uint32_t* status;          // pinned
   const void* cached_a[2];
   const void* cached_b[2];
+  uint32_t block_n;          // tile width: 256 when n is a multiple of it, else 128
   Sides sides;
 };
 
 int encode_weight_map(CUtensorMap* map, const void* base, uint64_t matrices, uint64_t n,
-                      uint64_t k_bytes) {
+                      uint64_t k_bytes, uint32_t block_n) {
   EncodeTiled encode = encode_tiled_entry();
   if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
   const cuuint64_t dimensions[3] = {k_bytes, n, matrices};
   const cuuint64_t strides[2] = {k_bytes, n * k_bytes};
-  const cuuint32_t box[3] = {kStageBytesK, kBlockN, 1u};
+  const cuuint32_t box[3] = {kStageBytesK, block_n, 1u};
   const cuuint32_t element_strides[3] = {1u, 1u, 1u};
   return static_cast<int>(encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3u, const_cast<void*>(base),
                                  dimensions, strides, box, element_strides,
@@ -572,9 +641,23 @@ int create(Mode mode, int groups, int matrices, int max_rows, int n, int k, bool
                                             sizeof(uint32_t), cudaHostAllocMapped));
   }
   if (status == 0) {
-    status = static_cast<int>(cudaFuncSetAttribute(grouped_fp4_kernel,
+    status = static_cast<int>(cudaFuncSetAttribute(grouped_fp4_kernel<128>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   Layout::kDynamicBytes));
+                                                   Layout<128>::kDynamicBytes));
+  }
+  if (status == 0) {
+    status = static_cast<int>(cudaFuncSetAttribute(grouped_fp4_kernel<256>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   Layout<256>::kDynamicBytes));
+  }
+  // 128-wide tiles by default. MIRCUDA_B200_GROUPED_FP4_BN=256 selects the wide ones where they
+  // tile N exactly: measured at the Qwen3-30B-A3B shapes they lose (gate_up with the fused
+  // epilogue 0.138 against 0.111 ms, down equal), because with one accumulator the epilogue no
+  // longer overlaps the next tile's MMAs and the epilogue, not the operand stream, is what a
+  // tile of these K extents waits for.
+  plan->block_n = 128u;
+  if (const char* forced = std::getenv("MIRCUDA_B200_GROUPED_FP4_BN")) {
+    if (std::atoi(forced) == 256 && n % 256 == 0) plan->block_n = 256u;
   }
   if (status != 0) {
     if (plan->records != nullptr) cudaFreeAsync(plan->records, plan->stream);
@@ -631,7 +714,7 @@ int bind_side(Plan* plan, int index, const Operands& operands) {
     plan->cached_a[index] = operands.a;
   }
   if (operands.b != plan->cached_b[index]) {
-    const int status = encode_weight_map(&side.b, operands.b, plan->matrices, plan->n, k_bytes);
+    const int status = encode_weight_map(&side.b, operands.b, plan->matrices, plan->n, k_bytes, plan->block_n);
     if (status != 0) return status;
     plan->cached_b[index] = operands.b;
   }
@@ -654,10 +737,17 @@ int bind_side(Plan* plan, int index, const Operands& operands) {
 }
 
 int run(Plan* plan, uint32_t side_count) {
-  grouped_fp4_kernel<<<plan->sm_count, kThreads, Layout::kDynamicBytes, plan->stream>>>(
-      plan->sides, side_count, plan->records, plan->total_tiles,
-      static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
-      static_cast<uint32_t>(plan->k), plan->status);
+  if (plan->block_n == 256u) {
+    grouped_fp4_kernel<256><<<plan->sm_count, kThreads, Layout<256>::kDynamicBytes, plan->stream>>>(
+        plan->sides, side_count, plan->records, plan->total_tiles,
+        static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
+        static_cast<uint32_t>(plan->k), plan->status);
+  } else {
+    grouped_fp4_kernel<128><<<plan->sm_count, kThreads, Layout<128>::kDynamicBytes, plan->stream>>>(
+        plan->sides, side_count, plan->records, plan->total_tiles,
+        static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
+        static_cast<uint32_t>(plan->k), plan->status);
+  }
   return static_cast<int>(cudaPeekAtLastError());
 }
 
@@ -675,7 +765,7 @@ int setup_variable(Plan* plan, const unsigned int* indices, const unsigned int* 
   if (indices == nullptr || rows == nullptr || offsets == nullptr || scale_offsets == nullptr) {
     return -1;
   }
-  const uint32_t tiles_n = (plan->n + kBlockN - 1u) / kBlockN;
+  const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
   grouped_fp4_variable_setup_kernel<<<1, 1024, 0, plan->stream>>>(
       indices, rows, offsets, scale_offsets, static_cast<uint32_t>(plan->groups),
       static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->max_rows), tiles_n,
@@ -779,7 +869,7 @@ extern "C" int mircuda_grouped_fp4_execute(void* raw, void* stream, const void* 
   if (status == 0) status = bind_side(plan, 0, Operands{a, a_scales, b, b_scales, alphas, c});
   if (status == 0 && selected == nullptr) status = -1;
   if (status != 0) return status;
-  const uint32_t tiles_n = (plan->n + kBlockN - 1u) / kBlockN;
+  const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
   grouped_fp4_indexed_setup_kernel<<<1, 1024, 0, plan->stream>>>(
       selected, static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->matrices),
       static_cast<uint32_t>(plan->max_rows), plan->broadcast_input, tiles_n, plan->records,
