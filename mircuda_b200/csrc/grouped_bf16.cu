@@ -296,6 +296,8 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
   } else {
     const uint32_t quarter = warp % 4u;
     uint32_t acc_stage = 0, acc_phase = 0;
+    // 32-byte stores need rows that start on 32-byte boundaries
+    const bool wide_stores = (n % 16u) == 0u && (reinterpret_cast<uintptr_t>(c) & 31u) == 0u;
     for (uint32_t index = blockIdx.x; index < tiles; index += gridDim.x) {
       const Tile tile = locate(index, starts, rows, offsets, groups, max_rows, BN);
       if (!ptx::mbarrier_wait(&acc_full[acc_stage], acc_phase, abort)) break;
@@ -313,6 +315,7 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
         if (row_valid && column < n) {
           __nv_bfloat16* destination = c_row + column;
           if (column + 32u <= n) {
+            uint32_t packed[16];
 #pragma unroll
             for (uint32_t part = 0; part < 4u; ++part) {
               float v[8];
@@ -328,14 +331,29 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
                       fmaf(beta, __uint_as_float(words[pair] & 0xffff0000u), v[pair * 2u + 1u]);
                 }
               }
-              uint32_t packed[4];
 #pragma unroll
               for (uint32_t pair = 0; pair < 4u; ++pair) {
                 const __nv_bfloat162 two = __floats2bfloat162_rn(v[pair * 2u], v[pair * 2u + 1u]);
-                packed[pair] = *reinterpret_cast<const uint32_t*>(&two);
+                packed[part * 4u + pair] = *reinterpret_cast<const uint32_t*>(&two);
               }
-              reinterpret_cast<uint4*>(destination)[part] =
-                  make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+            if (wide_stores) {
+              // 32 bytes per store fill whole sectors; 16-byte stores to the same rows cost twice
+              // the L1 -> L2 write traffic.
+#pragma unroll
+              for (uint32_t half = 0; half < 2u; ++half) {
+                asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(destination + half * 16u),
+                             "r"(packed[half * 8u + 0u]), "r"(packed[half * 8u + 1u]), "r"(packed[half * 8u + 2u]),
+                             "r"(packed[half * 8u + 3u]), "r"(packed[half * 8u + 4u]), "r"(packed[half * 8u + 5u]),
+                             "r"(packed[half * 8u + 6u]), "r"(packed[half * 8u + 7u])
+                             : "memory");
+              }
+            } else {
+#pragma unroll
+              for (uint32_t part = 0; part < 4u; ++part) {
+                reinterpret_cast<uint4*>(destination)[part] =
+                    make_uint4(packed[part * 4u], packed[part * 4u + 1u], packed[part * 4u + 2u], packed[part * 4u + 3u]);
+              }
             }
           } else {
 #pragma unroll
