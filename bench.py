@@ -438,7 +438,10 @@ def run_gpu(args) -> None:
     if world == 1 and not args.no_decode:
         import bench_decode
         with ClockSampler(local_rank) as decode_sampler:
-            results = bench_decode.run(["nvfp4"], 200, 5, hbm_peak, sampler=decode_sampler, echo=False)["results"]
+            everything = bench_decode.run(["nvfp4", "fp4"], 200, 5, hbm_peak, sampler=decode_sampler,
+                                          echo=False)["results"]
+        results = [record for record in everything if record["op"] == "nvfp4"]
+        fp4_results = [record for record in everything if record["op"] == "fp4"]
         fractions = [record["frac_of_measured_hbm"] for record in results]
         decode_record = {
             "op": "bf16 x NVFP4 GEMV (mircuda_b200_nvfp4_vector_*), Qwen3-8B weight shapes, M in {1,4,8}",
@@ -448,9 +451,15 @@ def run_gpu(args) -> None:
             "peak_gbs": hbm_peak, "peak_source": hbm_source,
             "min_frac": min(fractions), "mean_frac": sum(fractions) / len(fractions),
             "clocks": decode_sampler.summary(),
+            "launches": ("overlapped (programmatic dependent launch, the plans' default): a launch fetches "
+                         "weights while the previous one finishes; activations and outputs stay ordered"),
             "results": [{key: record[key] for key in ("shape", "m", "us", "gbs", "frac_of_measured_hbm",
                                                       "banks", "sm_mhz", "clock_samples")}
                         for record in results],
+            # the reference's own decode op, FP4 x FP4 at M = 1 (mircuda_fp4_vector_*), same method
+            "fp4_vector_results": [{key: record[key] for key in ("shape", "m", "us", "gbs",
+                                                                 "frac_of_measured_hbm", "banks", "sm_mhz")}
+                                   for record in fp4_results],
         }
     if world == 1 and not args.no_reference_kernels:
         import bench_decode

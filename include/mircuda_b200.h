@@ -108,7 +108,10 @@ void mircuda_fp4_destroy(void* plan);
 /* ----------------------------------------------------------- FP4 x FP4 GEMV (M = 1) ----
  * y[n] (bf16) = alpha * sum_k e2m1(x) e2m1(W) sx sw; k % 64 == 0.
  * Replaces sys/native/fp4_vector_sm120.cu:127-168, declared in
- * sys/src/platform/cutlass/fp4/vector.rs:11-29. */
+ * sys/src/platform/cutlass/fp4/vector.rs:11-29. With n % 128 == 0 and k % 2048 == 0 launches
+ * overlap as described for mircuda_b200_nvfp4_vector_* below (weights and weight scales are
+ * fetched early; MIRCUDA_B200_OVERLAP_LAUNCHES=0 serialises). execute returns -3 after a
+ * launch whose bounded wait ran out. */
 int mircuda_fp4_vector_create(int n, int k, void* stream, void** output);
 int mircuda_fp4_vector_execute(void* plan, void* stream, const void* input,
                                const void* input_scales, const void* weight,
@@ -418,7 +421,10 @@ void mircuda_dense_destroy(void* plan);
  * y[m, n] = f16(sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128]): x, y f16; weights [n, k/2]
  * bytes, even k in the low nibble, q in 0..15; scales f16 [n, k/128]. k % 128 == 0,
  * n % 8 == 0. m <= 16 streams the packed weights once (HBM-bound GEMV); larger m expands the
- * weights into a plan-owned f16 workspace (workspace_bytes) and runs the dense GEMM. */
+ * weights into a plan-owned f16 workspace (workspace_bytes) and runs the dense GEMM. At m <= 16
+ * with n % 16 == 0 and k % 2048 == 0 (the streaming kernel; `scales` must then be 4-byte
+ * aligned) launches overlap as described for mircuda_b200_nvfp4_vector_*: weights and scales
+ * are fetched while earlier work of the stream may still run. */
 int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void** output);
 size_t mircuda_b200_w4a16_workspace_bytes(const void* plan);
 int mircuda_b200_w4a16_execute(void* plan, void* stream, const void* input, const void* weight,
