@@ -26,6 +26,7 @@
 #include <cstdio>
 #include <cstdlib>
 
+#include "launch_overlap.hpp"
 #include "ptx.cuh"
 #include "ptx_pair.cuh"
 #include "tensor_map.hpp"
@@ -171,6 +172,10 @@ block_scaled_pair_gemm_kernel(const __grid_constant__ Maps maps, __nv_bfloat16* 
   ptx::cluster_wait();
   ptx::tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above touched no global memory and may have run beside the tail of the kernel
+  // before this one on the stream (the activation quantizer, normally); what follows may not.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
 
   const uint32_t tiles_m = (m + 2u * kBlockM - 1u) / (2u * kBlockM);
   const uint32_t tiles_n = (n + BN - 1u) / BN;
@@ -482,10 +487,19 @@ int launch(const Problem& problem, const Maps& maps, void* c, float alpha,
   uint32_t pairs = static_cast<uint32_t>(resident_pairs);
   if (tiles < pairs) pairs = tiles;
   const uint32_t k_stages = (problem.k + T::kElementsPerStage - 1u) / T::kElementsPerStage;
-  function<<<2u * pairs, kThreads, L::kDynamicBytes, problem.stream>>>(
-      maps, static_cast<__nv_bfloat16*>(c), problem.m, problem.n, k_stages, alpha, problem.status,
-      gather);
-  return static_cast<int>(cudaPeekAtLastError());
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(2u * pairs, 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.dynamicSmemBytes = L::kDynamicBytes;
+  config.stream = problem.stream;
+  cudaLaunchAttribute attribute = {};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = overlap_launches() ? 1u : 0u;
+  return static_cast<int>(cudaLaunchKernelEx(&config, function, maps, static_cast<__nv_bfloat16*>(c),
+                                             problem.m, problem.n, k_stages, alpha, problem.status,
+                                             gather));
 }
 
 }  // namespace pair_gemm

@@ -20,8 +20,14 @@
 
 #include <cstdint>
 
+#include <cstdlib>
+#include <cstring>
+#include <mutex>
+
 #include "fp4_codec.cuh"
+#include "launch_overlap.hpp"
 #include "marlin_common.cuh"
+#include "marlin_stream.hpp"
 #include "ptx.cuh"
 
 namespace mircuda_b200 {
@@ -229,6 +235,33 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
     status = static_cast<int>(cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device));
   }
   if (status != 0) return status;
+  // Shapes the streaming kernel covers go to it (MIRCUDA_B200_MARLIN_DENSE=tiles keeps the tile
+  // kernel below). Its bounded waits report through one pinned word per process: a launch whose
+  // wait ran out makes every later call return -3.
+  const char* choice = std::getenv("MIRCUDA_B200_MARLIN_DENSE");
+  if (choice == nullptr || std::strcmp(choice, "tiles") != 0) {
+    static std::mutex guard;
+    static uint32_t* stream_status = nullptr;
+    {
+      std::lock_guard<std::mutex> hold(guard);
+      if (stream_status == nullptr) {
+        void* memory = nullptr;
+        status = static_cast<int>(cudaHostAlloc(&memory, sizeof(uint32_t), cudaHostAllocPortable));
+        if (status != 0) return status;
+        stream_status = static_cast<uint32_t*>(memory);
+        *stream_status = 0u;
+      }
+    }
+    if (*reinterpret_cast<volatile uint32_t*>(stream_status) != 0u) return -3;
+    mircuda_b200::marlin_stream::Config config = {};
+    if ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0u && (reinterpret_cast<uintptr_t>(scales) & 7u) == 0u &&
+        (reinterpret_cast<uintptr_t>(temporary) & 15u) == 0u &&
+        mircuda_b200::marlin_stream::prepare(&config, tokens, output_features, input_features, sm_count) == 0) {
+      return mircuda_b200::marlin_stream::launch(
+          config, static_cast<cudaStream_t>(stream), mircuda_b200::overlap_launches(), input, weight, scales,
+          global_scale, output, temporary, locks, tokens, output_features, input_features, stream_status);
+    }
+  }
   const int tiles_n = output_features / kTileN;
   const int tiles_k = input_features / kTileK;
   // K slices: enough CTAs to fill the machine twice over, each with at least 8 K tiles.

@@ -12,7 +12,9 @@
 
 #include <cstdint>
 
+#include "launch_overlap.hpp"
 #include "layout.cuh"
+#include "ptx.cuh"
 
 namespace mircuda_b200 {
 namespace {
@@ -80,6 +82,10 @@ __global__ void __launch_bounds__(kThreads)
 mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
                       uint8_t* __restrict__ scales, uint32_t vectors, Divisor groups_per_row) {
   const uint32_t first = blockIdx.x * (kThreads * kVectorsPerThread) + threadIdx.x;
+  // The consumer of the codes (normally the GEMM) may set itself up while this grid runs;
+  // this grid waits for everything before it on the stream before its first access.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
 
   uint4 values[kVectorsPerThread];
 #pragma unroll
@@ -169,17 +175,19 @@ extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output,
   divisor.shift = 31u + log2_ceiling;
   divisor.magic = static_cast<uint32_t>(((1ull << divisor.shift) + divisor.divisor - 1u) /
                                         divisor.divisor);
-  auto cuda_stream = static_cast<cudaStream_t>(stream);
-  if (columns % 128u == 0u) {
-    mxfp8_quantize_kernel<true><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
-        static_cast<const uint4*>(input), static_cast<uint2*>(output),
-        static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor);
-  } else {
-    mxfp8_quantize_kernel<false><<<static_cast<unsigned int>(blocks), kThreads, 0, cuda_stream>>>(
-        static_cast<const uint4*>(input), static_cast<uint2*>(output),
-        static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor);
-  }
-  return static_cast<int>(cudaPeekAtLastError());
+  cudaLaunchConfig_t config = {};
+  config.gridDim = dim3(static_cast<unsigned int>(blocks), 1, 1);
+  config.blockDim = dim3(kThreads, 1, 1);
+  config.stream = static_cast<cudaStream_t>(stream);
+  cudaLaunchAttribute attribute = {};
+  attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attribute.val.programmaticStreamSerializationAllowed = 1;
+  config.attrs = &attribute;
+  config.numAttrs = overlap_launches() ? 1u : 0u;
+  auto function = columns % 128u == 0u ? mxfp8_quantize_kernel<true> : mxfp8_quantize_kernel<false>;
+  return static_cast<int>(cudaLaunchKernelEx(
+      &config, function, static_cast<const uint4*>(input), static_cast<uint2*>(output),
+      static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor));
 }
 
 extern "C" int mircuda_b200_mxfp8_swizzle_scales(const void* input, void* output, uint32_t rows,

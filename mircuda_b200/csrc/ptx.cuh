@@ -24,6 +24,20 @@ __device__ __forceinline__ bool elect_one() {
   return predicate != 0;
 }
 
+// ------------------------------------------------- programmatic dependent launch
+// A kernel launched with cudaLaunchAttributeProgrammaticStreamSerialization may start while the
+// kernel before it on the stream still runs; it must not touch global memory that kernel (or
+// anything before it) writes or reads-then-overwrites until dependency_wait() has returned.
+// Launched without the attribute, both instructions do nothing.
+
+__device__ __forceinline__ void dependency_launch_next() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+__device__ __forceinline__ void dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------------------- mbarrier
 
 __device__ __forceinline__ void mbarrier_init(uint64_t* barrier, uint32_t arrivals) {

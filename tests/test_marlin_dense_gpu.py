@@ -19,9 +19,20 @@ def pointer(tensor):
     return ctypes.c_void_p(tensor.data_ptr())
 
 
+@pytest.fixture(params=["stream", "tiles"])
+def dense_kernel(request, monkeypatch):
+    """Both kernels behind the entry point: the streaming one (default where N % 64 == 0 and
+    K % 512 == 0) and the tile kernel (every other shape, or by environment variable)."""
+    monkeypatch.setenv("MIRCUDA_B200_MARLIN_DENSE", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("tokens", [1, 8, 13, 16])
-@pytest.mark.parametrize("n,k", [(4096, 4096), (128, 64), (6144, 1024), (24576, 2048), (192, 1104)])
-def test_marlin_nvfp4_dense(cuda_stream, tokens, n, k):
+@pytest.mark.parametrize("n,k", [(4096, 4096), (128, 64), (6144, 1024), (24576, 2048), (192, 1104),
+                                 (4096, 12288), (6144, 4096), (64, 512), (24576, 4096), (9472, 1536)])
+def test_marlin_nvfp4_dense(cuda_stream, dense_kernel, tokens, n, k):
+    if dense_kernel == "tiles" and n * k > 24576 * 2048:
+        pytest.skip("the large shapes are there for the streaming kernel's K splits")
     from mircuda_b200 import _lib
     library = _lib.load()
     stream = ctypes.c_void_p(cuda_stream.cuda_stream)
