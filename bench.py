@@ -438,8 +438,8 @@ def run_gpu(args) -> None:
     if world == 1 and not args.no_decode:
         import bench_decode
         with ClockSampler(local_rank) as decode_sampler:
-            everything = bench_decode.run(["nvfp4", "fp4"], 200, 5, hbm_peak, sampler=decode_sampler,
-                                          echo=False)["results"]
+            everything = bench_decode.run(["nvfp4", "fp4", "marlin", "w4a16"], 200, 5, hbm_peak,
+                                          sampler=decode_sampler, echo=False)["results"]
         results = [record for record in everything if record["op"] == "nvfp4"]
         fp4_results = [record for record in everything if record["op"] == "fp4"]
         fractions = [record["frac_of_measured_hbm"] for record in results]
@@ -460,6 +460,14 @@ def run_gpu(args) -> None:
             "fp4_vector_results": [{key: record[key] for key in ("shape", "m", "us", "gbs",
                                                                  "frac_of_measured_hbm", "banks", "sm_mhz")}
                                    for record in fp4_results],
+            # the W4A16 decode paths: Marlin-layout NVFP4 (mircuda_marlin_nvfp4_dense_execute, M in
+            # {1,4,8}) and int4-g128 (mircuda_b200_w4a16_*, M in {1,16}; M = 256 is a GEMM, in TFLOP/s)
+            "marlin_results": [{key: record[key] for key in ("shape", "m", "us", "gbs",
+                                                             "frac_of_measured_hbm", "banks", "sm_mhz")}
+                               for record in everything if record["op"] == "marlin"],
+            "w4a16_results": [{key: record[key] for key in ("shape", "m", "us", "gbs", "frac_of_measured_hbm",
+                                                            "banks", "sm_mhz", "tflops") if key in record}
+                              for record in everything if record["op"] == "w4a16"],
         }
     if world == 1 and not args.no_reference_kernels:
         import bench_decode

@@ -462,7 +462,15 @@ int mircuda_marlin_prepare_moe_routes(void* stream, const void* selected, const 
  * are the caller-owned reduction workspace of the reference interface; `thread_config` and
  * `atomic_reduce` are accepted and ignored (one tile geometry, ordered reduction).
  * Replaces sys/native/marlin/dense_kernel.cu:73-102, declared in
- * sys/src/platform/marlin/execute/dense.rs:16-31. n % 64 == 0, k % 16 == 0. */
+ * sys/src/platform/marlin/execute/dense.rs:16-31. n % 64 == 0, k % 16 == 0.
+ * Shapes with k % 512 == 0 (weights 16-byte, scales 8-byte, `temporary` 16-byte aligned) run on
+ * a streaming kernel that converts the activations bf16 -> f16 (saturating at +-65504) and is
+ * launched so that it may overlap the tail of the previous kernel on the stream: it reads
+ * `weight` and `scales` before that kernel has completed, everything else after; a kernel that
+ * writes the prepared weights must therefore not be the one directly before this call
+ * (MIRCUDA_B200_OVERLAP_LAUNCHES=0 serialises the launch, MIRCUDA_B200_MARLIN_DENSE=tiles keeps
+ * the tile kernel for every shape). Returns -3 on every call after a launch whose bounded wait
+ * ran out. */
 int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* input, const void* weight,
                                        void* output, void* temporary, const void* scales,
                                        const float* global_scale, int tokens,

@@ -66,6 +66,8 @@ def test_cuda_arm_line():
     decode = record["decode"]
     assert len(decode["results"]) == 12 and 0.0 < decode["min_frac"] <= decode["mean_frac"] < 1.2
     assert {entry["m"] for entry in decode["results"]} == {1, 4, 8}
+    assert len(decode["fp4_vector_results"]) == 4 and len(decode["marlin_results"]) == 12
+    assert {entry["m"] for entry in decode["w4a16_results"]} == {1, 16, 256}
     # the reference's own kernels beside this library's (present when oracle/_ref was built)
     for entry in record["reference_kernels"]["results"]:
         assert entry["us"] > 0 and entry["reference_us"] > 0

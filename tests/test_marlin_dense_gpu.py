@@ -57,6 +57,9 @@ def test_marlin_nvfp4_dense(cuda_stream, dense_kernel, tokens, n, k):
     assert library.mircuda_marlin_nvfp4_prepare_scales(
         stream, pointer(d_scales), None, pointer(d_global), pointer(prepared),
         pointer(prepared_global), pointer(maximum), 1, n, k) == 0
+    # The streaming kernel may read the prepared weights before the kernel directly in front of
+    # it on the stream has completed (the entry point's documented contract): finish preparing.
+    cuda_stream.synchronize()
     for _ in range(2):                                   # twice: locks must return to zero
         assert library.mircuda_marlin_nvfp4_dense_execute(
             stream, pointer(x), pointer(packed), pointer(out), pointer(temporary), pointer(prepared),

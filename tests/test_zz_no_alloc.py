@@ -2,9 +2,10 @@
 
 Some hosts forbid this library from calling the CUDA allocator (their own arena owns all
 device memory); for them ``mircuda_b200_fp4_vector_execute_static`` keeps its scratch in a
-fixed device array inside the library. It runs the same kernel as
-``mircuda_fp4_vector_execute``, so the two must agree; the check is made on two calls in a
-row because the static scratch keeps the previous call's contents. Collected last on
+fixed device array inside the library. It computes what ``mircuda_fp4_vector_execute``
+computes (whichever kernel the plan picks for the shape), so the two must agree; the check is
+made on several calls in a row, a large shape before and after smaller ones and one that needs
+no scratch at all (k <= 512), because the static scratch keeps the previous call's contents. Collected last on
 purpose (file name), and written to pass both alone in a fresh process and after the rest
 of the suite.
 """
@@ -33,7 +34,7 @@ def test_static_entry_point_matches_plan_entry_point(cuda_stream):
     from mircuda_b200 import _lib, plans
     library = _lib.load()
     stream = ctypes.c_void_p(cuda_stream.cuda_stream)
-    for call, (n, k) in enumerate([(4096, 4096), (200, 1088)]):   # two calls in a row
+    for call, (n, k) in enumerate([(4096, 4096), (200, 1088), (256, 512), (4096, 4096)]):   # calls in a row
         x, xs = random_fp4(1, k, 31 + call)
         w, ws = random_fp4(n, k, 41 + call)
         tensors = [u8(x.reshape(-1)), u8(xs), u8(w.reshape(-1)), u8(ws)]
