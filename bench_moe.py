@@ -12,8 +12,9 @@ the whole layer of `mircuda_b200.moe` (count exchange, dispatch of the routed ro
 experts' owners, two grouped GEMMs with SwiGLU between them, weighted collection of the
 results); the router's output is prepared once, outside the timed region. One JSON line per
 mode: `value` = 2*assignments*(gate_up + down) flop of all ranks over the step time (max over
-ranks, CUDA events); `gemm` = the same flop over the summed durations of the two grouped GEMM
-launches on rank 0 (the grouped kernel alone); the bytes a rank moves over NVLink each way are
+ranks, CUDA events, no other instrumentation in that loop); `gemm` = the same flop over the
+summed durations of the two grouped GEMM launches on rank 0 (the grouped kernel alone, from a
+second loop with an event pair around every stage); the bytes a rank moves over NVLink each way are
 reported beside them.
 """
 from __future__ import annotations
@@ -38,8 +39,8 @@ EXPERTS, TOP_K, HIDDEN, INTERMEDIATE, TOKENS = 128, 8, 2048, 768, 4096
 def main() -> None:
     parser = argparse.ArgumentParser()
     parser.add_argument("--mode", default="both", choices=["bf16", "nvfp4", "both"])
-    parser.add_argument("--steps", type=int, default=50)
-    parser.add_argument("--warmup", type=int, default=5)
+    parser.add_argument("--steps", type=int, default=200)
+    parser.add_argument("--warmup", type=int, default=20)
     parser.add_argument("--transport", default="peer", choices=["peer", "nccl"],
                         help="peer: this library's dispatch/collect kernels over NVLink peer memory; "
                              "nccl: all_to_all_single of padded blocks")
@@ -128,8 +129,9 @@ def main() -> None:
             with torch.cuda.stream(stream):
                 graph.replay()
             barrier()
-        else:
-            layer.gemm_events = []
+        # The layer is timed without instrumentation; a second loop of the same length records an
+        # event pair around every stage for the per-stage and per-GEMM figures.
+        layer.gemm_events = None
         begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(stream):
             begin.record(stream)
@@ -141,6 +143,12 @@ def main() -> None:
             end.record(stream)
         barrier()
         elapsed_ms = begin.elapsed_time(end)
+        if graph is None:
+            layer.gemm_events = []
+            with torch.cuda.stream(stream):
+                for _ in range(args.steps):
+                    layer.forward(x, dispatch, weights)
+            barrier()
         if world > 1:
             tensor = torch.tensor([elapsed_ms], device=device)
             dist.all_reduce(tensor, op=dist.ReduceOp.MAX)

@@ -4,6 +4,12 @@
 // points; numerics follow that kernel (each 16-wide dot is formed exactly, then scaled by
 // the product of the two block scales and accumulated in fp32).
 //
+// Three kernels sit behind the plan: shapes with n % 128 == 0 and k % 2048 == 0 run on the
+// streaming kernel of nvfp4_stream.cu (the activation vector dequantised into its MMA fragments;
+// MIRCUDA_B200_FP4_VECTOR=stream, the default there), fp4_vector_tc.cu is the tcgen05 kernel
+// (=tensor) and the CUDA-core kernel of this file (=simt) serves every other shape and the
+// allocation-free entry point.
+//
 // The op streams 0.5625*N*K bytes once and is bound by HBM. Work is cut into tiles of
 // 128 rows (one scale row-tile) by 512 K-elements (eight whole 512-byte scale atoms), one CTA
 // per tile, so that every weight byte arrives through 16-byte loads with all of a tile's

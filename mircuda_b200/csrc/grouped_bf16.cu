@@ -24,6 +24,7 @@
 #include <cstdlib>
 #include <new>
 
+#include "launch_overlap.hpp"
 #include "ptx.cuh"
 #include "tensor_map.hpp"
 
@@ -68,6 +69,10 @@ grouped_bf16_setup_kernel(const unsigned int* __restrict__ rows,
                           uint32_t* __restrict__ tile_starts) {
   __shared__ uint32_t warp_totals[32];
   __shared__ uint32_t carry;
+  // The routing arrays come from the kernel before this one; the main kernel after this one may
+  // set itself up meanwhile.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   if (threadIdx.x == 0) carry = 0u;
   __syncthreads();
   for (uint32_t base = 0; base < groups; base += 1024u) {
@@ -182,6 +187,10 @@ grouped_bf16_kernel(const __grid_constant__ MapSet maps, const unsigned int* __r
     ptx::tmem_allocate(tmem_slot, kTmemColumns);
     ptx::tmem_relinquish();
   }
+  // Barriers, tensor memory and the tensor-map prefetch above needed nothing from global memory
+  // and may have run beside the set-up kernel; its tile starts are read from here on.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   uint32_t* starts_table = reinterpret_cast<uint32_t*>(shared + L::kStartsOffset);
   const uint32_t* starts = tile_starts;
   if (groups <= L::kSharedGroups) {
@@ -429,11 +438,11 @@ int launch(Plan* plan, const unsigned int* rows, const unsigned int* offsets,
     if (status != 0) return status;
     configured_device = plan->device;
   }
-  function<<<plan->sm_count, kThreads, L::kDynamicBytes, plan->stream>>>(
-      plan->maps, rows, offsets, indices, plan->tile_starts, static_cast<__nv_bfloat16*>(c),
-      static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->max_rows),
-      static_cast<uint32_t>(plan->n), static_cast<uint32_t>(plan->k), beta, plan->status);
-  return static_cast<int>(cudaPeekAtLastError());
+  return launch_after_dependency(function, dim3(plan->sm_count), dim3(kThreads), L::kDynamicBytes, plan->stream,
+                                 plan->maps, rows, offsets, indices, plan->tile_starts,
+                                 static_cast<__nv_bfloat16*>(c), static_cast<uint32_t>(plan->groups),
+                                 static_cast<uint32_t>(plan->max_rows), static_cast<uint32_t>(plan->n),
+                                 static_cast<uint32_t>(plan->k), beta, plan->status);
 }
 
 }  // namespace grouped_bf16
@@ -518,10 +527,10 @@ int execute(void* raw, void* stream, const void* input, const void* weights,
     plan->cached_weights = weights;
   }
   const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
-  grouped_bf16_setup_kernel<<<1, 1024, 0, cuda_stream>>>(
-      rows, indices, static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->groups),
-      static_cast<uint32_t>(plan->max_rows), tiles_n, plan->tile_starts);
-  int status = static_cast<int>(cudaPeekAtLastError());
+  int status = launch_after_dependency(grouped_bf16_setup_kernel, dim3(1), dim3(1024), 0, cuda_stream, rows,
+                                       indices, static_cast<uint32_t>(plan->matrices),
+                                       static_cast<uint32_t>(plan->groups),
+                                       static_cast<uint32_t>(plan->max_rows), tiles_n, plan->tile_starts);
   if (status != 0) return status;
   return plan->block_n == 128u ? launch<128u, 6u, 4u>(plan, rows, offsets, indices, output, beta)
                                : launch<256u, 4u, 2u>(plan, rows, offsets, indices, output, beta);

@@ -29,6 +29,7 @@
 #include <cstdlib>
 #include <new>
 
+#include "launch_overlap.hpp"
 #include "layout.cuh"
 #include "nvfp4_block.cuh"
 #include "ptx.cuh"
@@ -165,6 +166,10 @@ grouped_fp4_variable_setup_kernel(const unsigned int* __restrict__ indices,
                                   const unsigned int* __restrict__ scale_offsets, uint32_t groups,
                                   uint32_t matrices, uint32_t max_rows, uint32_t tiles_n,
                                   Group* __restrict__ records, uint32_t* __restrict__ total_tiles) {
+  // The routing arrays come from the kernel before this one; the main kernel after this one may
+  // set itself up meanwhile.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   scan_groups(groups, tiles_n, records, total_tiles, [&](uint32_t group) {
     Group record = {};
     record.matrix = indices[group];
@@ -181,6 +186,8 @@ grouped_fp4_indexed_setup_kernel(const unsigned int* __restrict__ selected, uint
                                  uint32_t matrices, uint32_t m, bool broadcast_input,
                                  uint32_t tiles_n, Group* __restrict__ records,
                                  uint32_t* __restrict__ total_tiles) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   scan_groups(groups, tiles_n, records, total_tiles, [&](uint32_t group) {
     const uint32_t input_group = broadcast_input ? 0u : group;
     Group record = {};
@@ -280,6 +287,10 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
     ptx::tmem_allocate(tmem_slot, kTmemColumns);
     ptx::tmem_relinquish();
   }
+  // Barriers, tensor memory and the tensor-map prefetch above needed nothing from global memory
+  // and may have run beside the set-up kernel; its records are read from here on.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   uint32_t* starts_table = reinterpret_cast<uint32_t*>(shared + L::kStartsOffset);
   const uint32_t* shared_starts = groups <= L::kSharedGroups ? starts_table : nullptr;
   if (shared_starts != nullptr) {
@@ -737,18 +748,13 @@ int bind_side(Plan* plan, int index, const Operands& operands) {
 }
 
 int run(Plan* plan, uint32_t side_count) {
-  if (plan->block_n == 256u) {
-    grouped_fp4_kernel<256><<<plan->sm_count, kThreads, Layout<256>::kDynamicBytes, plan->stream>>>(
-        plan->sides, side_count, plan->records, plan->total_tiles,
-        static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
-        static_cast<uint32_t>(plan->k), plan->status);
-  } else {
-    grouped_fp4_kernel<128><<<plan->sm_count, kThreads, Layout<128>::kDynamicBytes, plan->stream>>>(
-        plan->sides, side_count, plan->records, plan->total_tiles,
-        static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
-        static_cast<uint32_t>(plan->k), plan->status);
-  }
-  return static_cast<int>(cudaPeekAtLastError());
+  const bool wide = plan->block_n == 256u;
+  return launch_after_dependency(wide ? grouped_fp4_kernel<256> : grouped_fp4_kernel<128>,
+                                 dim3(plan->sm_count), dim3(kThreads),
+                                 wide ? Layout<256>::kDynamicBytes : Layout<128>::kDynamicBytes, plan->stream,
+                                 plan->sides, side_count, plan->records, plan->total_tiles,
+                                 static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
+                                 static_cast<uint32_t>(plan->k), plan->status);
 }
 
 int check(void* raw, void* stream, Mode mode, Plan** plan) {
@@ -766,11 +772,10 @@ int setup_variable(Plan* plan, const unsigned int* indices, const unsigned int* 
     return -1;
   }
   const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
-  grouped_fp4_variable_setup_kernel<<<1, 1024, 0, plan->stream>>>(
-      indices, rows, offsets, scale_offsets, static_cast<uint32_t>(plan->groups),
-      static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->max_rows), tiles_n,
-      plan->records, plan->total_tiles);
-  return static_cast<int>(cudaPeekAtLastError());
+  return launch_after_dependency(grouped_fp4_variable_setup_kernel, dim3(1), dim3(1024), 0, plan->stream, indices,
+                                 rows, offsets, scale_offsets, static_cast<uint32_t>(plan->groups),
+                                 static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->max_rows),
+                                 tiles_n, plan->records, plan->total_tiles);
 }
 
 }  // namespace grouped_fp4
@@ -870,11 +875,10 @@ extern "C" int mircuda_grouped_fp4_execute(void* raw, void* stream, const void* 
   if (status == 0 && selected == nullptr) status = -1;
   if (status != 0) return status;
   const uint32_t tiles_n = (plan->n + plan->block_n - 1u) / plan->block_n;
-  grouped_fp4_indexed_setup_kernel<<<1, 1024, 0, plan->stream>>>(
-      selected, static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->matrices),
-      static_cast<uint32_t>(plan->max_rows), plan->broadcast_input, tiles_n, plan->records,
-      plan->total_tiles);
-  status = static_cast<int>(cudaPeekAtLastError());
+  status = mircuda_b200::launch_after_dependency(grouped_fp4_indexed_setup_kernel, dim3(1), dim3(1024), 0, plan->stream,
+                                   selected, static_cast<uint32_t>(plan->groups),
+                                   static_cast<uint32_t>(plan->matrices), static_cast<uint32_t>(plan->max_rows),
+                                   plan->broadcast_input, tiles_n, plan->records, plan->total_tiles);
   if (status == 0) status = run(plan, 1u);
   return status;
 }

@@ -237,7 +237,9 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
   if (status != 0) return status;
   // Shapes the streaming kernel covers go to it (MIRCUDA_B200_MARLIN_DENSE=tiles keeps the tile
   // kernel below). Its bounded waits report through one pinned word per process: a launch whose
-  // wait ran out makes every later call return -3.
+  // wait ran out makes every later call return -3. The word is allocated by the first call that
+  // is not being captured into a graph; until it exists (a first call under capture) the kernel
+  // runs without a place to report to.
   const char* choice = std::getenv("MIRCUDA_B200_MARLIN_DENSE");
   if (choice == nullptr || std::strcmp(choice, "tiles") != 0) {
     static std::mutex guard;
@@ -245,14 +247,18 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
     {
       std::lock_guard<std::mutex> hold(guard);
       if (stream_status == nullptr) {
-        void* memory = nullptr;
-        status = static_cast<int>(cudaHostAlloc(&memory, sizeof(uint32_t), cudaHostAllocPortable));
-        if (status != 0) return status;
-        stream_status = static_cast<uint32_t*>(memory);
-        *stream_status = 0u;
+        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
+        if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capture) == cudaSuccess &&
+            capture == cudaStreamCaptureStatusNone) {
+          void* memory = nullptr;
+          status = static_cast<int>(cudaHostAlloc(&memory, sizeof(uint32_t), cudaHostAllocPortable));
+          if (status != 0) return status;
+          stream_status = static_cast<uint32_t*>(memory);
+          *stream_status = 0u;
+        }
       }
     }
-    if (*reinterpret_cast<volatile uint32_t*>(stream_status) != 0u) return -3;
+    if (stream_status != nullptr && *reinterpret_cast<volatile uint32_t*>(stream_status) != 0u) return -3;
     mircuda_b200::marlin_stream::Config config = {};
     if ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0u && (reinterpret_cast<uintptr_t>(scales) & 7u) == 0u &&
         (reinterpret_cast<uintptr_t>(temporary) & 15u) == 0u &&

@@ -463,7 +463,7 @@ marlin_stream_kernel(const __nv_bfloat16* __restrict__ input, const uint8_t* __r
     copy_async_wait<0>();      // nothing of this CTA is in flight when it leaves
   }
   __syncthreads();
-  if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
+  if (threadIdx.x == 0 && *abort != 0u && status != nullptr) *status = 1u;
 }
 
 using Kernel = void (*)(const __nv_bfloat16*, const uint8_t*, const uint8_t*, const float*, __nv_bfloat16*,
@@ -541,9 +541,25 @@ int prepare(Config* config, int tokens, int n, int k, int sm_count) {
     }
   }
   if (best < 0.0) return -1;
-  return static_cast<int>(cudaFuncSetAttribute(pick(config->row_groups, config->chunks_per_warp),
-                                               cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                               shared_bytes(config->row_groups)));
+  // The shared-memory attribute is set once per kernel, device and thread.
+  static thread_local int configured_device = -1;
+  static thread_local unsigned configured = 0u;      // bit = row_groups * 16 + chunks
+  int device = 0;
+  int status = static_cast<int>(cudaGetDevice(&device));
+  if (status != 0) return status;
+  if (device != configured_device) {
+    configured_device = device;
+    configured = 0u;
+  }
+  const unsigned bit = 1u << ((config->row_groups - 1) * 16 + config->chunks_per_warp);
+  if ((configured & bit) == 0u) {
+    status = static_cast<int>(cudaFuncSetAttribute(pick(config->row_groups, config->chunks_per_warp),
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   shared_bytes(config->row_groups)));
+    if (status != 0) return status;
+    configured |= bit;
+  }
+  return 0;
 }
 
 int launch(const Config& config, cudaStream_t stream, bool overlap_launches, const void* input,

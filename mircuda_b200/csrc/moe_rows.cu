@@ -16,10 +16,18 @@
 
 #include <cstdint>
 
+#include "launch_overlap.hpp"
+#include "ptx.cuh"
+
 namespace mircuda_b200 {
 namespace moe_rows {
 
 constexpr int kThreads = 256;
+
+// Every kernel here begins with a dependency wait and is launched with programmatic stream
+// serialisation (launch_after_dependency): its CTAs may be scheduled while the kernel before it on
+// the stream is finishing, but touch no global memory until that kernel has completed. A layer is
+// a chain of a dozen launches of a few microseconds each; this takes the launch latency out of it.
 
 __device__ __forceinline__ float2 unpack(uint32_t pair) {
   return make_float2(__uint_as_float(pair << 16), __uint_as_float(pair & 0xffff0000u));
@@ -35,6 +43,8 @@ __global__ void __launch_bounds__(kThreads)
 moe_scatter_rows_kernel(const uint4* __restrict__ source, const int* __restrict__ source_index,
                         const int* __restrict__ destination_index, uint4* __restrict__ destination,
                         uint32_t count, uint32_t pieces) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t item = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; item < count; item += warps) {
@@ -79,6 +89,8 @@ __global__ void __launch_bounds__(kThreads)
 moe_combine_rows_kernel(const uint4* __restrict__ rows, const int* __restrict__ index,
                         const float* __restrict__ weights, uint4* __restrict__ output,
                         uint32_t tokens, uint32_t top_k, uint32_t pieces) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t token = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; token < tokens; token += warps) {
@@ -109,6 +121,8 @@ moe_combine_rows_kernel(const uint4* __restrict__ rows, const int* __restrict__ 
 __global__ void moe_group_offsets_kernel(const int* __restrict__ counts, unsigned int* __restrict__ rows,
                                          unsigned int* __restrict__ offsets, uint32_t blocks,
                                          uint32_t per_block, uint32_t block_rows, uint32_t align) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   const uint32_t block = blockIdx.x * blockDim.x + threadIdx.x;
   if (block >= blocks) return;
   uint32_t cursor = block * block_rows;
@@ -137,6 +151,8 @@ __global__ void moe_expert_layout_kernel(const int* __restrict__ all_counts, uin
                                          unsigned int* __restrict__ offsets,
                                          unsigned int* __restrict__ received_rows,
                                          uint32_t capacity_rows, unsigned int* __restrict__ overflow) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   extern __shared__ uint32_t totals[];
   const uint32_t expert = threadIdx.x;
   uint32_t total = 0u, before_me = 0u;
@@ -181,6 +197,8 @@ moe_dispatch_rows_kernel(const uint4* __restrict__ source, const int* __restrict
                          const int* __restrict__ base_for_me, const PeerBases receive,
                          int* __restrict__ remote_row, uint32_t count, uint32_t local_experts,
                          uint32_t pieces, uint32_t capacity_rows) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t item = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; item < count; item += warps) {
@@ -211,6 +229,8 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
                         const int* __restrict__ sorted_expert, const int* __restrict__ remote_row,
                         const float* __restrict__ weights, uint4* __restrict__ output,
                         uint32_t tokens, uint32_t top_k, uint32_t local_experts, uint32_t pieces) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
   for (uint32_t token = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; token < tokens; token += warps) {
@@ -259,6 +279,8 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
 __global__ void __launch_bounds__(kThreads)
 moe_scale_atoms_kernel(const uint4* __restrict__ input, uint8_t* __restrict__ output, uint32_t rows,
                        const unsigned int* __restrict__ row_bound, uint32_t columns) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   if (row_bound != nullptr) rows = min(rows, __ldg(row_bound));
   const uint32_t vectors = columns / 16u;
   const size_t total = static_cast<size_t>(rows) * vectors;
@@ -301,11 +323,10 @@ extern "C" int mircuda_b200_moe_scatter_rows_bf16(const void* source, const int*
     return -1;
   }
   if (count == 0) return 0;
-  moe_scatter_rows_kernel<<<grid_for(count, kThreads / 32), kThreads, 0,
-                            static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(source), source_index, destination_index,
-      static_cast<uint4*>(destination), count, columns / 8u);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_scatter_rows_kernel, dim3(grid_for(count, kThreads / 32)), dim3(kThreads),
+                                 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(source),
+                                 source_index, destination_index, static_cast<uint4*>(destination), count,
+                                 columns / 8u);
 }
 
 extern "C" int mircuda_b200_moe_swiglu_bf16(const void* input, void* output, uint32_t rows,
@@ -318,10 +339,9 @@ extern "C" int mircuda_b200_moe_swiglu_bf16(const void* input, void* output, uin
   }
   if (rows == 0) return 0;
   const size_t total = static_cast<size_t>(rows) * (intermediate / 8u);
-  moe_swiglu_kernel<<<grid_for(total, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(input), static_cast<uint4*>(output), rows, row_bound,
-      intermediate / 8u);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_swiglu_kernel, dim3(grid_for(total, kThreads)), dim3(kThreads), 0,
+                                 static_cast<cudaStream_t>(stream), static_cast<const uint4*>(input),
+                                 static_cast<uint4*>(output), rows, row_bound, intermediate / 8u);
 }
 
 extern "C" int mircuda_b200_moe_combine_rows_bf16(const void* rows, const int* index,
@@ -334,11 +354,9 @@ extern "C" int mircuda_b200_moe_combine_rows_bf16(const void* rows, const int* i
     return -1;
   }
   if (tokens == 0) return 0;
-  moe_combine_rows_kernel<<<grid_for(tokens, kThreads / 32), kThreads, 0,
-                            static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(rows), index, weights, static_cast<uint4*>(output), tokens, top_k,
-      columns / 8u);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_combine_rows_kernel, dim3(grid_for(tokens, kThreads / 32)), dim3(kThreads),
+                                 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(rows), index,
+                                 weights, static_cast<uint4*>(output), tokens, top_k, columns / 8u);
 }
 
 extern "C" int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* rows,
@@ -350,9 +368,9 @@ extern "C" int mircuda_b200_moe_group_offsets(const int* counts, unsigned int* r
       align == 0) {
     return -1;
   }
-  moe_group_offsets_kernel<<<(blocks + 63u) / 64u, 64, 0, static_cast<cudaStream_t>(stream)>>>(
-      counts, rows, offsets, blocks, per_block, block_rows, align);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_group_offsets_kernel, dim3((blocks + 63u) / 64u), dim3(64), 0,
+                                 static_cast<cudaStream_t>(stream), counts, rows, offsets, blocks, per_block,
+                                 block_rows, align);
 }
 
 extern "C" int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t world, uint32_t rank,
@@ -366,10 +384,10 @@ extern "C" int mircuda_b200_moe_expert_layout(const int* all_counts, uint32_t wo
       experts % world != 0 || align == 0 || capacity_rows == 0 || capacity_rows > 0x7fffffffu) {
     return -1;
   }
-  moe_expert_layout_kernel<<<1, experts, experts * sizeof(uint32_t), static_cast<cudaStream_t>(stream)>>>(
-      all_counts, world, rank, experts, experts / world, align, base_for_me, rows, offsets,
-      received_rows, capacity_rows, overflow);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_expert_layout_kernel, dim3(1), dim3(experts), experts * sizeof(uint32_t),
+                                 static_cast<cudaStream_t>(stream), all_counts, world, rank, experts,
+                                 experts / world, align, base_for_me, rows, offsets, received_rows, capacity_rows,
+                                 overflow);
 }
 
 extern "C" int mircuda_b200_moe_dispatch_rows_bf16(
@@ -389,11 +407,10 @@ extern "C" int mircuda_b200_moe_dispatch_rows_bf16(
     receive.base[peer] = receive_buffers[peer];
   }
   if (count == 0) return 0;
-  moe_dispatch_rows_kernel<<<grid_for(count, kThreads / 32), kThreads, 0,
-                             static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(source), source_index, sorted_expert, position, base_for_me, receive,
-      remote_row, count, local_experts, columns / 8u, capacity_rows);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_dispatch_rows_kernel, dim3(grid_for(count, kThreads / 32)), dim3(kThreads),
+                                 0, static_cast<cudaStream_t>(stream), static_cast<const uint4*>(source),
+                                 source_index, sorted_expert, position, base_for_me, receive, remote_row, count,
+                                 local_experts, columns / 8u, capacity_rows);
 }
 
 extern "C" int mircuda_b200_moe_collect_rows_bf16(
@@ -414,16 +431,10 @@ extern "C" int mircuda_b200_moe_collect_rows_bf16(
   if (tokens == 0) return 0;
   const int grid = grid_for(tokens, kThreads / 32);
   auto cuda_stream = static_cast<cudaStream_t>(stream);
-  if (top_k <= 8) {
-    moe_collect_rows_kernel<8><<<grid, kThreads, 0, cuda_stream>>>(
-        results, slot, sorted_expert, remote_row, weights, static_cast<uint4*>(output), tokens, top_k,
-        local_experts, columns / 8u);
-  } else {
-    moe_collect_rows_kernel<32><<<grid, kThreads, 0, cuda_stream>>>(
-        results, slot, sorted_expert, remote_row, weights, static_cast<uint4*>(output), tokens, top_k,
-        local_experts, columns / 8u);
-  }
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(top_k <= 8 ? moe_collect_rows_kernel<8> : moe_collect_rows_kernel<32>,
+                                 dim3(grid), dim3(kThreads), 0, cuda_stream, results, slot, sorted_expert,
+                                 remote_row, weights, static_cast<uint4*>(output), tokens, top_k, local_experts,
+                                 columns / 8u);
 }
 
 extern "C" int mircuda_b200_moe_scale_atoms(const void* row_scales, void* atoms, uint32_t rows,
@@ -435,7 +446,7 @@ extern "C" int mircuda_b200_moe_scale_atoms(const void* row_scales, void* atoms,
     return -1;
   }
   const size_t total = static_cast<size_t>(rows) * (columns / 16u);
-  moe_scale_atoms_kernel<<<grid_for(total, kThreads), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const uint4*>(row_scales), static_cast<uint8_t*>(atoms), rows, row_bound, columns);
-  return static_cast<int>(cudaPeekAtLastError());
+  return mircuda_b200::launch_after_dependency(moe_scale_atoms_kernel, dim3(grid_for(total, kThreads)), dim3(kThreads), 0,
+                                 static_cast<cudaStream_t>(stream), static_cast<const uint4*>(row_scales),
+                                 static_cast<uint8_t*>(atoms), rows, row_bound, columns);
 }

@@ -12,8 +12,10 @@
 #include <cstdint>
 
 #include "fp4_codec.cuh"
+#include "launch_overlap.hpp"
 #include "layout.cuh"
 #include "nvfp4_block.cuh"
+#include "ptx.cuh"
 
 namespace mircuda_b200 {
 namespace {
@@ -59,6 +61,10 @@ __global__ void __launch_bounds__(256)
 nvfp4_quantize_kernel(const uint4* __restrict__ input, const float* __restrict__ global_scale,
                 uint2* __restrict__ codes, uint8_t* __restrict__ scales, uint32_t rows,
                 const unsigned int* __restrict__ row_bound, uint32_t k) {
+  // Launched so that it may be scheduled while the kernel before it is finishing; nothing is
+  // read before that kernel has completed.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   if (row_bound != nullptr) rows = min(rows, __ldg(row_bound));
   const uint32_t blocks_per_row = k / 16u;
   const size_t block = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -126,11 +132,11 @@ int launch_quantize(const void* input, const void* global_scale, void* codes, vo
   const size_t blocks = static_cast<size_t>(rows) * (k / 16u);
   const size_t grid = (blocks + 255u) / 256u;
   if (grid > 0x7fffffffull) return -1;
-  nvfp4_quantize_kernel<ROW_MAJOR_SCALES, SWIGLU>
-      <<<static_cast<unsigned int>(grid), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-          static_cast<const uint4*>(input), static_cast<const float*>(global_scale),
-          static_cast<uint2*>(codes), static_cast<uint8_t*>(scales), rows, row_bound, k);
-  return static_cast<int>(cudaPeekAtLastError());
+  return launch_after_dependency(nvfp4_quantize_kernel<ROW_MAJOR_SCALES, SWIGLU>,
+                                 dim3(static_cast<unsigned int>(grid)), dim3(256), 0,
+                                 static_cast<cudaStream_t>(stream), static_cast<const uint4*>(input),
+                                 static_cast<const float*>(global_scale), static_cast<uint2*>(codes),
+                                 static_cast<uint8_t*>(scales), rows, row_bound, k);
 }
 
 }  // namespace

@@ -6,6 +6,12 @@
 // (exact weight * scale products, fp32 accumulation, global scale before the bf16 round)
 // it follows.
 //
+// Three kernels sit behind the plan. Shapes with n % 128 == 0 and k % 2048 == 0 run on the
+// streaming kernel of nvfp4_stream.cu (MIRCUDA_B200_NVFP4_VECTOR=stream, the default there); the
+// two kernels of this file serve every other shape: `nvfp4_direct_kernel` (global loads through
+// a register pipeline; the default among the two) and `nvfp4_vector_kernel` (the TMA-fed ring
+// described next; MIRCUDA_B200_NVFP4_VECTOR=ring).
+//
 // The op streams 0.5625*N*K bytes once and is bound by HBM, so the kernel is built around
 // keeping bytes in flight rather than around arithmetic:
 //  * a CTA owns one 128-row scale tile and a contiguous part of K; a producer warp streams

@@ -25,7 +25,9 @@ HERE = Path(__file__).resolve().parent
 BUILD_DIR = HERE / "_build"
 REF_DIR = HERE / "_ref"
 ORACLE_LIB = BUILD_DIR / "libmircuda_oracle.so"
-REFERENCE_ROOT = Path(os.environ.get("MIRCUDA_REFERENCE_ROOT", "/root/reference"))
+# The reference checkout: MIRCUDA_REFERENCE_ROOT, else a directory named `reference` beside this
+# repository. When neither exists the prebuilt files in `_ref/` are used as they are.
+REFERENCE_ROOT = Path(os.environ.get("MIRCUDA_REFERENCE_ROOT", HERE.parent.parent / "reference"))
 GENCODE = "arch=compute_100a,code=sm_100a"
 
 
@@ -62,7 +64,13 @@ def build_oracle(force: bool = False) -> Path:
 
 
 def _cutlass_include() -> list[str]:
-    """Header-only CUTLASS tree the reference's vector kernels include (bfloat16.h, float8.h)."""
+    """Header-only CUTLASS tree the reference's vector kernels include (bfloat16.h, float8.h):
+    MIRCUDA_CUTLASS_ROOT (a checkout with `include/` and `tools/util/include/`), else the tree an
+    installed flashinfer wheel carries."""
+    override = os.environ.get("MIRCUDA_CUTLASS_ROOT")
+    if override:
+        paths = [Path(override) / "include", Path(override) / "tools" / "util" / "include"]
+        return [f"-I{path}" for path in paths if path.exists()]
     try:
         import flashinfer  # noqa: F401  (only for its vendored header tree)
         root = Path(flashinfer.__file__).resolve().parent / "data" / "cutlass"
