@@ -43,7 +43,9 @@ constexpr uint32_t kStageBytesK = 128;     // 256 E2M1 codes per stage row
 constexpr uint32_t kStageElements = 256;
 constexpr uint32_t kAtomBytes = 512;
 constexpr uint32_t kAtomsK = 4;            // scale atoms (64 K-elements each) per stage
-constexpr uint32_t kThreads = 192;
+// Warps: TMA producer, MMA issuer, then one or two sets of four epilogue warps (a warp reads the
+// tensor-memory lanes of quarter warp % 4; two sets split a tile's columns between them).
+constexpr uint32_t threads_for(uint32_t epilogue_sets) { return (2u + 4u * epilogue_sets) * 32u; }
 constexpr uint32_t kTmemColumns = 512;
 constexpr uint32_t kPieceMaps = 8;         // A tensor maps with box rows 128, 64, ..., 1
 
@@ -243,14 +245,15 @@ __device__ __forceinline__ Tile locate(uint32_t index, const Group* __restrict__
   return tile;
 }
 
-template <uint32_t BN>
-__global__ void __launch_bounds__(kThreads, 1)
+template <uint32_t BN, uint32_t SETS>
+__global__ void __launch_bounds__(threads_for(SETS), 1)
 grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
                    const Group* __restrict__ records, const uint32_t* __restrict__ total_tiles,
                    uint32_t groups, uint32_t n, uint32_t k, uint32_t* __restrict__ status) {
   using L = Layout<BN>;
   constexpr uint32_t kStages = L::kStages;
   constexpr uint32_t kAccStages = L::kAccStages;
+  constexpr uint32_t kThreads = threads_for(SETS);
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t misalignment = ptx::smem_address(dynamic_shared) & 1023u;
   uint8_t* shared = dynamic_shared + ((1024u - misalignment) & 1023u);
@@ -275,7 +278,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
     }
     for (uint32_t stage = 0; stage < kAccStages; ++stage) {
       ptx::mbarrier_init(&acc_full[stage], 1);
-      ptx::mbarrier_init(&acc_empty[stage], 4);
+      ptx::mbarrier_init(&acc_empty[stage], 4u * SETS);
     }
     *abort = 0u;
     ptx::fence_barrier_init();
@@ -442,6 +445,7 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
   } else {
     // ---------------------------------------------------------------------- epilogue
     const uint32_t quarter = warp % 4u;
+    const uint32_t set = (warp - 2u) / 4u;          // which share of the tile's columns
     const bool vector_stores = (n % 8u) == 0u;
     uint32_t acc_stage = 0, acc_phase = 0;
     // 32-byte stores need rows that start on 32-byte boundaries (n % 16 == 0 and such a base)
@@ -538,14 +542,15 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
       // Pieces alternate between two register buffers: the tensor-memory load of the next piece
       // is in flight while this one is converted and stored. The accumulator goes back to the
       // MMA warp as soon as its last piece has been read.
-      constexpr uint32_t kPieces = BN / 32u;
+      constexpr uint32_t kSetPieces = BN / 32u / SETS;
+      const uint32_t first_piece = set * kSetPieces, kPieces = first_piece + kSetPieces;
       uint32_t even[32], odd[32];
-      ptx::tmem_load_32x32(tmem_row, even);
+      ptx::tmem_load_32x32(tmem_row + first_piece * 32u, even);
       ptx::tmem_load_wait();
 #pragma unroll 1
-      for (uint32_t chunk = 0; chunk < kPieces; chunk += 2u) {
+      for (uint32_t chunk = first_piece; chunk < kPieces; chunk += 2u) {
         ptx::tmem_load_32x32(tmem_row + (chunk + 1u) * 32u, odd);
-        if (chunk == 0u) {
+        if (chunk == first_piece) {
           // first use of the wait: fetch the next tile's record behind the loads already issued
           const uint32_t following = index + gridDim.x;
           if (following < tiles) {
@@ -587,6 +592,14 @@ grouped_fp4_kernel(const __grid_constant__ Sides sides, uint32_t side_count,
 
 enum class Mode { kVariable, kPaired, kIndexed };
 
+using Kernel = void (*)(const Sides, uint32_t, const Group*, const uint32_t*, uint32_t, uint32_t, uint32_t,
+                        uint32_t*);
+
+inline Kernel kernel_for(bool wide, uint32_t epilogue_sets) {
+  if (wide) return epilogue_sets == 2u ? grouped_fp4_kernel<256, 2> : grouped_fp4_kernel<256, 1>;
+  return epilogue_sets == 2u ? grouped_fp4_kernel<128, 2> : grouped_fp4_kernel<128, 1>;
+}
+
 struct Plan {
   Mode mode;
   int groups, matrices, max_rows, n, k;
@@ -599,6 +612,7 @@ struct Plan {
   const void* cached_a[2];
   const void* cached_b[2];
   uint32_t block_n;          // tile width: 256 when n is a multiple of it, else 128
+  uint32_t epilogue_sets;    // sets of four epilogue warps: 1 or 2, 0 = chosen per launch
   Sides sides;
 };
 
@@ -651,15 +665,11 @@ int create(Mode mode, int groups, int matrices, int max_rows, int n, int k, bool
     status = static_cast<int>(cudaHostAlloc(reinterpret_cast<void**>(&plan->status),
                                             sizeof(uint32_t), cudaHostAllocMapped));
   }
-  if (status == 0) {
-    status = static_cast<int>(cudaFuncSetAttribute(grouped_fp4_kernel<128>,
+  for (uint32_t variant = 0; variant < 4u && status == 0; ++variant) {
+    status = static_cast<int>(cudaFuncSetAttribute(kernel_for(variant / 2u != 0u, variant % 2u + 1u),
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   Layout<128>::kDynamicBytes));
-  }
-  if (status == 0) {
-    status = static_cast<int>(cudaFuncSetAttribute(grouped_fp4_kernel<256>,
-                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   Layout<256>::kDynamicBytes));
+                                                   variant / 2u != 0u ? Layout<256>::kDynamicBytes
+                                                                      : Layout<128>::kDynamicBytes));
   }
   // 128-wide tiles by default. MIRCUDA_B200_GROUPED_FP4_BN=256 selects the wide ones where they
   // tile N exactly: measured at the Qwen3-30B-A3B shapes they lose (gate_up with the fused
@@ -669,6 +679,12 @@ int create(Mode mode, int groups, int matrices, int max_rows, int n, int k, bool
   plan->block_n = 128u;
   if (const char* forced = std::getenv("MIRCUDA_B200_GROUPED_FP4_BN")) {
     if (std::atoi(forced) == 256 && n % 256 == 0) plan->block_n = 256u;
+  }
+  // Epilogue warps: chosen per launch (see run()); MIRCUDA_B200_GROUPED_FP4_EPILOGUE=4 or 8 forces one or two sets.
+  plan->epilogue_sets = 0u;
+  if (const char* forced = std::getenv("MIRCUDA_B200_GROUPED_FP4_EPILOGUE")) {
+    if (std::atoi(forced) == 8) plan->epilogue_sets = 2u;
+    if (std::atoi(forced) == 4) plan->epilogue_sets = 1u;
   }
   if (status != 0) {
     if (plan->records != nullptr) cudaFreeAsync(plan->records, plan->stream);
@@ -749,8 +765,12 @@ int bind_side(Plan* plan, int index, const Operands& operands) {
 
 int run(Plan* plan, uint32_t side_count) {
   const bool wide = plan->block_n == 256u;
-  return launch_after_dependency(wide ? grouped_fp4_kernel<256> : grouped_fp4_kernel<128>,
-                                 dim3(plan->sm_count), dim3(kThreads),
+  // Two sets of epilogue warps where the epilogue also does SwiGLU and the requantisation
+  // (measured: gate_up 0.116 -> 0.112 ms); one set for plain bf16 outputs, where eight warps
+  // storing at once were slower (down 0.081 -> 0.086 ms).
+  const uint32_t sets = plan->epilogue_sets != 0u ? plan->epilogue_sets
+                                                  : (plan->sides.side[0].codes != nullptr ? 2u : 1u);
+  return launch_after_dependency(kernel_for(wide, sets), dim3(plan->sm_count), dim3(threads_for(sets)),
                                  wide ? Layout<256>::kDynamicBytes : Layout<128>::kDynamicBytes, plan->stream,
                                  plan->sides, side_count, plan->records, plan->total_tiles,
                                  static_cast<uint32_t>(plan->groups), static_cast<uint32_t>(plan->n),
