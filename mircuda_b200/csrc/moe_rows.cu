@@ -222,18 +222,25 @@ moe_dispatch_rows_kernel(const uint4* __restrict__ source, const int* __restrict
 // buffers (peer loads) and adds them with its routing weights. slot[t, j] is the position of
 // (token, choice) in the expert-sorted assignment list.
 // All top_k rows of a piece are requested before the first is used: their row indices and
-// weights are read once per token (lane j holds choice j) and broadcast.
+// weights are read once per token (lane j holds choice j) and broadcast. A token's row is cut
+// into `parts` runs of pieces, one warp each, so that a rank with few tokens (an 8-GPU job has
+// 512) still has thousands of loads in flight.
 template <int TOP_K>
 __global__ void __launch_bounds__(kThreads)
 moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
                         const int* __restrict__ sorted_expert, const int* __restrict__ remote_row,
                         const float* __restrict__ weights, uint4* __restrict__ output,
-                        uint32_t tokens, uint32_t top_k, uint32_t local_experts, uint32_t pieces) {
+                        uint32_t tokens, uint32_t top_k, uint32_t local_experts, uint32_t pieces,
+                        uint32_t parts) {
   ptx::dependency_launch_next();
   ptx::dependency_wait();
   const uint32_t warps = gridDim.x * (kThreads / 32);
   const uint32_t lane = threadIdx.x % 32u;
-  for (uint32_t token = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; token < tokens; token += warps) {
+  const uint32_t part_pieces = (pieces + parts - 1u) / parts;
+  for (uint32_t item = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; item < tokens * parts; item += warps) {
+    const uint32_t token = item / parts;
+    const uint32_t first_piece = (item % parts) * part_pieces;
+    const uint32_t end_piece = min(pieces, first_piece + part_pieces);
     const uint4* my_row = nullptr;
     float my_weight = 0.0f;
     if (lane < top_k) {
@@ -245,7 +252,7 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
         my_weight = __ldg(weights + token * top_k + lane);
       }
     }
-    for (uint32_t piece = lane; piece < pieces; piece += 32u) {
+    for (uint32_t piece = first_piece + lane; piece < end_piece; piece += 32u) {
       uint4 values[TOP_K];
       float scale[TOP_K];
 #pragma unroll
@@ -429,12 +436,16 @@ extern "C" int mircuda_b200_moe_collect_rows_bf16(
     results.base[peer] = result_buffers[peer];
   }
   if (tokens == 0) return 0;
-  const int grid = grid_for(tokens, kThreads / 32);
+  // Warps per token: enough for about 4096 warps in all, each with at least 32 pieces.
+  const uint32_t pieces = columns / 8u;
+  uint32_t parts = 1u;
+  while (parts < 8u && tokens * parts < 4096u && pieces / (parts * 2u) >= 32u) parts *= 2u;
+  const int grid = grid_for(static_cast<size_t>(tokens) * parts, kThreads / 32);
   auto cuda_stream = static_cast<cudaStream_t>(stream);
   return mircuda_b200::launch_after_dependency(top_k <= 8 ? moe_collect_rows_kernel<8> : moe_collect_rows_kernel<32>,
                                  dim3(grid), dim3(kThreads), 0, cuda_stream, results, slot, sorted_expert,
                                  remote_row, weights, static_cast<uint4*>(output), tokens, top_k, local_experts,
-                                 columns / 8u);
+                                 pieces, parts);
 }
 
 extern "C" int mircuda_b200_moe_scale_atoms(const void* row_scales, void* atoms, uint32_t rows,
