@@ -29,6 +29,7 @@
 #include "ptx_pair.cuh"
 #include "tensor_map.hpp"
 #include "w4a16_stream.hpp"
+#include "w4a16_tile.hpp"
 
 extern "C" int mircuda_dense_create(int input_type, int output_type, int m, int n, int k,
                                     void* stream, void** output);
@@ -356,6 +357,8 @@ struct Plan {
   bool stream_kernel;        // the persistent streaming kernel of w4a16_stream.cu
   bool overlap_launches;
   w4a16_stream::Config stream_config;
+  bool tile_kernel;          // the fused prefill GEMM of w4a16_tile.cu
+  w4a16_tile::Config tile_config;
 };
 
 int parts_for(int n, int k, int slots, int max_parts) {
@@ -453,6 +456,17 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
       plan->parts = parts_for(n, k, sm_count, SharedLayout<2>::kMaxParts);
     }
   } else if (status == 0 && m > kVectorTokens) {
+    // Prefill runs on the fused GEMM of w4a16_tile.cu (the packed weights are expanded inside the
+    // kernel); MIRCUDA_B200_W4A16_PREFILL=expand keeps the two-launch form below (expansion into
+    // an f16 workspace, then the dense GEMM), which is also the fallback.
+    const char* choice = std::getenv("MIRCUDA_B200_W4A16_PREFILL");
+    if (!(choice != nullptr && std::strcmp(choice, "expand") == 0) &&
+        mircuda_b200::w4a16_tile::eligible(m, n, k)) {
+      status = mircuda_b200::w4a16_tile::prepare(&plan->tile_config, m, n, k);
+      plan->tile_kernel = status == 0;
+    }
+  }
+  if (status == 0 && m > kVectorTokens && !plan->tile_kernel) {
     status = mircuda_dense_create(0, 0, m, n, k, stream, &plan->dense);
     if (status == 0) {
       status = static_cast<int>(cudaMallocAsync(reinterpret_cast<void**>(&plan->expanded),
@@ -498,6 +512,10 @@ extern "C" int mircuda_b200_w4a16_execute(void* raw, void* stream, const void* i
     if ((reinterpret_cast<uintptr_t>(scales) & 3u) != 0u) return -1;
     return mircuda_b200::w4a16_stream::launch(&plan->stream_config, cuda_stream, plan->overlap_launches, input, weight,
                                 scales, output, plan->m, plan->n, plan->k, plan->status);
+  }
+  if (plan->tile_kernel) {
+    return mircuda_b200::w4a16_tile::launch(&plan->tile_config, cuda_stream, input, weight, scales, output,
+                                            plan->m, plan->n, plan->k, plan->status);
   }
   if (plan->dense != nullptr) {
     const size_t words = static_cast<size_t>(plan->n) * plan->k / 8u;

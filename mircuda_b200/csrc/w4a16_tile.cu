@@ -1,0 +1,399 @@
+// int4-g128 W4A16 GEMM for prefill (M > 16): C[M,N] = A[M,K] . dequant(W)[N,K]^T, f16 activations
+// and outputs, fp32 accumulation in tensor memory, with the expansion of the 4-bit weights fused
+// into the GEMM: the packed weights are read from HBM once per tile and never exist as f16 in
+// global memory. (The two-launch form, expansion into an f16 workspace and then the dense GEMM,
+// reads and writes that workspace once more per call and took as long for the expansion as for
+// the GEMM.)
+//
+// One persistent 320-thread CTA per SM, tiles of 128 tokens x BN weight rows, 64 K-elements per
+// stage:
+//  * warp 0 issues the TMA loads of a stage: the activation tile (128 rows x 128 bytes,
+//    128-byte swizzle) and the packed weight tile (BN rows x 32 bytes, no swizzle);
+//  * warps 6-9 (one thread per weight row, two rows for BN = 256) turn a row's 32 packed bytes
+//    into 64 f16 values (nibble OR-ed into the mantissa of 1024.0, minus 1032 = q - 8 exactly,
+//    times the group's f16 scale: the value the two-launch form stores) and write them as the
+//    K-major, 128-byte-swizzled B tile the tensor core reads: 16-byte piece c of row r goes to
+//    r * 128 + ((c ^ (r % 8)) * 16);
+//  * warp 1 issues four tcgen05.mma (kind::f16) per stage once both operands are in place;
+//  * warps 2-5 drain the accumulator (32 columns at a time) to f16 outputs.
+// Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag, every role
+// leaves its loop, tensor memory is freed and *status is set.
+#include <cuda.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+#include "launch_overlap.hpp"
+#include "ptx.cuh"
+#include "tensor_map.hpp"
+#include "w4a16_tile.hpp"
+
+namespace mircuda_b200 {
+namespace w4a16_tile {
+
+constexpr uint32_t kBlockM = 128;
+constexpr uint32_t kBlockK = 64;           // K-elements per stage: 128 bytes of f16, 32 of int4
+constexpr uint32_t kGroupK = 128;          // elements per scale group: two stages
+constexpr uint32_t kThreads = 320;
+constexpr uint32_t kConverterThreads = 128;
+constexpr uint32_t kTmemColumns = 512;
+
+template <uint32_t BN, uint32_t STAGES>
+struct Layout {
+  static constexpr uint32_t kAccStages = 2;
+  static constexpr uint32_t kABytes = kBlockM * 128u;
+  static constexpr uint32_t kBBytes = BN * 128u;
+  static constexpr uint32_t kPackedBytes = BN * 32u;
+  static constexpr uint32_t kBOffset = STAGES * kABytes;
+  static constexpr uint32_t kPackedOffset = kBOffset + STAGES * kBBytes;
+  static constexpr uint32_t kBarrierOffset = kPackedOffset + STAGES * kPackedBytes;
+  static constexpr uint32_t kBarriers = 3 * STAGES + 2 * kAccStages;
+  static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
+  static constexpr uint32_t kDynamicBytes = kMiscOffset + 16 + 1024;
+  static_assert(kAccStages * BN <= kTmemColumns, "tensor memory budget");
+  static_assert(kDynamicBytes <= 232448, "shared memory budget");
+};
+
+__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
+  uint32_t d;
+  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+
+// Eight codes of one word (k ascending from the low nibble) -> (q - 8) * scale as four f16x2 in
+// K order. 0x6400 is 1024.0 in f16: OR-ing a nibble into its mantissa gives 1024 + q exactly.
+__device__ __forceinline__ uint4 expand8(uint32_t codes, uint32_t scale2) {
+  constexpr uint32_t kMask = 0x000f000fu, kMagic = 0x64006400u, kBias = 0x64086408u;   // 1032.0
+  const uint32_t v04 = mul_f16x2(sub_f16x2((codes & kMask) | kMagic, kBias), scale2);           // k0, k4
+  const uint32_t v15 = mul_f16x2(sub_f16x2(((codes >> 4) & kMask) | kMagic, kBias), scale2);    // k1, k5
+  const uint32_t v26 = mul_f16x2(sub_f16x2(((codes >> 8) & kMask) | kMagic, kBias), scale2);    // k2, k6
+  const uint32_t v37 = mul_f16x2(sub_f16x2(((codes >> 12) & kMask) | kMagic, kBias), scale2);   // k3, k7
+  return make_uint4(prmt(v04, v15, 0x5410u), prmt(v26, v37, 0x5410u), prmt(v04, v15, 0x7632u),
+                    prmt(v26, v37, 0x7632u));
+}
+
+__device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "r"(address)
+               : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void store_shared_16(uint32_t address, uint4 v) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
+
+template <uint32_t BN, uint32_t STAGES>
+__global__ void __launch_bounds__(kThreads, 1)
+w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                  const __half* __restrict__ scales, __half* __restrict__ c, uint32_t m, uint32_t n,
+                  uint32_t k, uint32_t idesc, uint32_t* __restrict__ status) {
+  using L = Layout<BN, STAGES>;
+  constexpr uint32_t kAccStages = L::kAccStages;
+  extern __shared__ uint8_t dynamic_shared[];
+  const uint32_t misalignment = ptx::smem_address(dynamic_shared) & 1023u;
+  uint8_t* shared = dynamic_shared + ((1024u - misalignment) & 1023u);
+  uint8_t* shared_a = shared;
+  uint8_t* shared_b = shared + L::kBOffset;
+  uint8_t* shared_packed = shared + L::kPackedOffset;
+  uint64_t* loaded = reinterpret_cast<uint64_t*>(shared + L::kBarrierOffset);   // TMA -> converters
+  uint64_t* converted = loaded + STAGES;                                         // converters -> MMA
+  uint64_t* empty = converted + STAGES;                                          // MMA -> TMA
+  uint64_t* acc_full = empty + STAGES;
+  uint64_t* acc_empty = acc_full + kAccStages;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(shared + L::kMiscOffset);
+  volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
+
+  const uint32_t warp = threadIdx.x / 32u;
+  const uint32_t lane = threadIdx.x % 32u;
+
+  if (threadIdx.x == 0) {
+    for (uint32_t stage = 0; stage < STAGES; ++stage) {
+      ptx::mbarrier_init(&loaded[stage], 1);
+      ptx::mbarrier_init(&converted[stage], kConverterThreads / 32u);
+      ptx::mbarrier_init(&empty[stage], 1);
+    }
+    for (uint32_t stage = 0; stage < kAccStages; ++stage) {
+      ptx::mbarrier_init(&acc_full[stage], 1);
+      ptx::mbarrier_init(&acc_empty[stage], 4);
+    }
+    *abort = 0u;
+    ptx::fence_barrier_init();
+    ptx::fence_proxy_async();
+    ptx::prefetch_tensor_map(&map_a);
+    ptx::prefetch_tensor_map(&map_w);
+  }
+  if (warp == 1) {
+    ptx::tmem_allocate(tmem_slot, kTmemColumns);
+    ptx::tmem_relinquish();
+  }
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  ptx::tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  // Nothing above touched global memory; the rest runs after the kernel before this one.
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
+
+  const uint32_t tiles_m = (m + kBlockM - 1u) / kBlockM;
+  const uint32_t tiles_n = (n + BN - 1u) / BN;
+  const uint32_t tiles = tiles_m * tiles_n;
+  const uint32_t k_tiles = k / kBlockK;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA producer
+    if (ptx::elect_one()) {
+      uint32_t stage = 0, phase = 0;
+      bool running = true;
+      for (uint32_t tile = blockIdx.x; running && tile < tiles; tile += gridDim.x) {
+        const uint32_t m0 = (tile % tiles_m) * kBlockM;
+        const uint32_t n0 = (tile / tiles_m) * BN;
+        for (uint32_t kt = 0; kt < k_tiles; ++kt) {
+          if (!ptx::mbarrier_wait(&empty[stage], phase ^ 1u, abort)) {
+            running = false;
+            break;
+          }
+          ptx::mbarrier_arrive_expect_tx(&loaded[stage], L::kABytes + L::kPackedBytes);
+          ptx::tma_load_2d(shared_a + stage * L::kABytes, &map_a, &loaded[stage],
+                           static_cast<int32_t>(kt * kBlockK), static_cast<int32_t>(m0));
+          ptx::tma_load_2d(shared_packed + stage * L::kPackedBytes, &map_w, &loaded[stage],
+                           static_cast<int32_t>(kt * (kBlockK / 2u)), static_cast<int32_t>(n0));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (*abort != 0u) {
+        for (int spin = 0; spin < 256; ++spin) __nanosleep(1000);
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (ptx::elect_one()) {
+      uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
+      bool running = true;
+      for (uint32_t tile = blockIdx.x; running && tile < tiles; tile += gridDim.x) {
+        if (!ptx::mbarrier_wait(&acc_empty[acc_stage], acc_phase ^ 1u, abort)) break;
+        ptx::tcgen05_fence_after();
+        const uint32_t d_tmem = tmem_base + acc_stage * BN;
+        for (uint32_t kt = 0; kt < k_tiles; ++kt) {
+          // The converters arrive after the stage's loads have landed, so one wait covers both.
+          if (!ptx::mbarrier_wait(&converted[stage], phase, abort)) {
+            running = false;
+            break;
+          }
+          ptx::tcgen05_fence_after();
+          const uint64_t a_descriptor =
+              ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_a + stage * L::kABytes));
+          const uint64_t b_descriptor =
+              ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_b + stage * L::kBBytes));
+#pragma unroll
+          for (uint32_t kb = 0; kb < 4u; ++kb) {
+            ptx::mma_f16(d_tmem, a_descriptor + 2u * kb, b_descriptor + 2u * kb, idesc, (kt | kb) != 0u);
+          }
+          ptx::tcgen05_commit(&empty[stage]);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!running) break;
+        ptx::tcgen05_commit(&acc_full[acc_stage]);
+        if (++acc_stage == kAccStages) {
+          acc_stage = 0;
+          acc_phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp < 6u) {
+    // ------------------------------------------------------------------ epilogue
+    const uint32_t quarter = warp % 4u;
+    uint32_t acc_stage = 0, acc_phase = 0;
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      const uint32_t m0 = (tile % tiles_m) * kBlockM;
+      const uint32_t n0 = (tile / tiles_m) * BN;
+      if (!ptx::mbarrier_wait(&acc_full[acc_stage], acc_phase, abort)) break;
+      ptx::tcgen05_fence_after();
+      const uint32_t row = m0 + quarter * 32u + lane;
+      const uint32_t tmem_row = tmem_base + ((quarter * 32u) << 16) + acc_stage * BN;
+#pragma unroll 1
+      for (uint32_t chunk = 0; chunk < BN / 32u; ++chunk) {
+        uint32_t values[32];
+        ptx::tmem_load_32x32(tmem_row + chunk * 32u, values);
+        ptx::tmem_load_wait();
+        const uint32_t column = n0 + chunk * 32u;
+        if (row < m && column < n) {
+          __half* destination = c + static_cast<size_t>(row) * n + column;
+          if (column + 32u <= n) {       // n % 8 == 0 and a 16-byte aligned base: 16-byte stores
+#pragma unroll
+            for (uint32_t part = 0; part < 4u; ++part) {
+              uint32_t packed[4];
+#pragma unroll
+              for (uint32_t pair = 0; pair < 4u; ++pair) {
+                const __half2 two = __floats2half2_rn(__uint_as_float(values[part * 8u + pair * 2u]),
+                                                      __uint_as_float(values[part * 8u + pair * 2u + 1u]));
+                packed[pair] = *reinterpret_cast<const uint32_t*>(&two);
+              }
+              reinterpret_cast<uint4*>(destination)[part] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            }
+          } else {
+#pragma unroll
+            for (uint32_t item = 0; item < 32u; ++item) {
+              if (column + item < n) destination[item] = __float2half_rn(__uint_as_float(values[item]));
+            }
+          }
+        }
+      }
+      ptx::tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) ptx::mbarrier_arrive(&acc_empty[acc_stage]);
+      if (++acc_stage == kAccStages) {
+        acc_stage = 0;
+        acc_phase ^= 1u;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ converters
+    const uint32_t thread = threadIdx.x - 6u * 32u;          // 0..127
+    const uint32_t groups = k / kGroupK;
+    constexpr uint32_t kParts = BN / kConverterThreads;      // weight rows per thread
+    uint32_t stage = 0, phase = 0;
+    bool alive = true;
+    // The scale of a row's group is fetched one group ahead of its use (a group is two stages).
+    // Rows past N hold zero codes (TMA fill) and get a zero scale; nothing stores them.
+    auto fetch_scale = [&](uint32_t tile, uint32_t group, uint32_t part) -> uint32_t {
+      const uint32_t row = (tile / tiles_m) * BN + part * kConverterThreads + thread;
+      if (tile >= tiles || row >= n) return 0u;
+      return static_cast<uint32_t>(__half_as_ushort(__ldg(scales + static_cast<size_t>(row) * groups + group)));
+    };
+    uint32_t upcoming[kParts];
+#pragma unroll
+    for (uint32_t part = 0; part < kParts; ++part) upcoming[part] = fetch_scale(blockIdx.x, 0u, part);
+    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+      uint32_t scale2[kParts] = {};
+      for (uint32_t kt = 0; kt < k_tiles; ++kt) {
+        if ((kt & 1u) == 0u) {
+          const uint32_t group = kt / 2u;
+#pragma unroll
+          for (uint32_t part = 0; part < kParts; ++part) {
+            scale2[part] = upcoming[part] * 0x00010001u;
+            upcoming[part] = group + 1u < groups ? fetch_scale(tile, group + 1u, part)
+                                                 : fetch_scale(tile + gridDim.x, 0u, part);
+          }
+        }
+        // (Once a wait has run out, `abort` is raised and this thread skips every later wait: the
+        // loops run to their end on meaningless data and the launch reports the failure.)
+        if (alive) alive = ptx::mbarrier_wait(&loaded[stage], phase, abort);
+        const uint32_t packed_base = ptx::smem_address(shared_packed + stage * L::kPackedBytes);
+        const uint32_t b_base = ptx::smem_address(shared_b + stage * L::kBBytes);
+#pragma unroll
+        for (uint32_t part = 0; part < kParts; ++part) {
+          const uint32_t row = part * kConverterThreads + thread;
+          const uint4 low = load_shared_16(packed_base + row * 32u);
+          const uint4 high = load_shared_16(packed_base + row * 32u + 16u);
+          const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
+          const uint32_t row_base = b_base + row * 128u;
+          const uint32_t swizzle = row % 8u;
+#pragma unroll
+          for (uint32_t piece = 0; piece < 8u; ++piece) {
+            store_shared_16(row_base + ((piece ^ swizzle) * 16u), expand8(words[piece], scale2[part]));
+          }
+        }
+        // The tensor core reads shared memory through the async proxy: make this thread's
+        // stores visible to it, then one arrival per warp.
+        ptx::fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) ptx::mbarrier_arrive(&converted[stage]);
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  }
+
+  ptx::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    __syncwarp();
+    ptx::tcgen05_fence_after();
+    ptx::tmem_deallocate(tmem_base, kTmemColumns);
+  }
+  if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
+}
+
+constexpr uint32_t kBlockN = 256;
+constexpr uint32_t kStages = 4;
+
+bool eligible(int m, int n, int k) { return m > 0 && n > 0 && n % 8 == 0 && k > 0 && k % kGroupK == 0; }
+
+int prepare(Config* config, int m, int n, int k) {
+  if (!eligible(m, n, k)) return -1;
+  int device = 0;
+  int status = static_cast<int>(cudaGetDevice(&device));
+  if (status == 0) {
+    status = static_cast<int>(cudaDeviceGetAttribute(&config->sm_count, cudaDevAttrMultiProcessorCount, device));
+  }
+  if (status == 0) {
+    status = static_cast<int>(cudaFuncSetAttribute(w4a16_tile_kernel<kBlockN, kStages>,
+                                                   cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                   Layout<kBlockN, kStages>::kDynamicBytes));
+  }
+  config->cached_input = nullptr;
+  config->cached_weight = nullptr;
+  return status;
+}
+
+int launch(Config* config, cudaStream_t stream, const void* input, const void* weight, const void* scales,
+           void* output, int m, int n, int k, uint32_t* status_word) {
+  if (input != config->cached_input) {
+    const int status = encode_k_major_map(&config->map_a, input, m, k, 2u, kBlockM);
+    if (status != 0) return status;
+    config->cached_input = input;
+  }
+  if (weight != config->cached_weight) {
+    // Packed weights as bytes [N, K / 2]; a box is 32 bytes (64 codes) of BN rows, not swizzled.
+    EncodeTiled encode = encode_tiled_entry();
+    if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
+    const cuuint64_t dimensions[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(n)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
+    const cuuint32_t box[2] = {kBlockK / 2u, kBlockN};
+    const cuuint32_t element_strides[2] = {1u, 1u};
+    const int status = static_cast<int>(encode(
+        &config->map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2u, const_cast<void*>(weight), dimensions, strides, box,
+        element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE,
+        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE));
+    if (status != 0) return status;
+    config->cached_weight = weight;
+  }
+  const uint32_t tiles = ((static_cast<uint32_t>(m) + kBlockM - 1u) / kBlockM) *
+                         ((static_cast<uint32_t>(n) + kBlockN - 1u) / kBlockN);
+  const uint32_t grid = tiles < static_cast<uint32_t>(config->sm_count) ? tiles : config->sm_count;
+  const uint32_t idesc = ptx::make_f16_idesc(false, kBlockM, kBlockN);
+  return launch_after_dependency(w4a16_tile_kernel<kBlockN, kStages>, dim3(grid), dim3(kThreads),
+                                 Layout<kBlockN, kStages>::kDynamicBytes, stream, config->map_a, config->map_w,
+                                 static_cast<const __half*>(scales), static_cast<__half*>(output),
+                                 static_cast<uint32_t>(m), static_cast<uint32_t>(n), static_cast<uint32_t>(k),
+                                 idesc, status_word);
+}
+
+}  // namespace w4a16_tile
+}  // namespace mircuda_b200

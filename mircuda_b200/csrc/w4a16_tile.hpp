@@ -1,0 +1,32 @@
+// Internal interface of the fused int4 W4A16 prefill GEMM (w4a16_tile.cu), used by the plan entry
+// points in w4a16_int4.cu.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_runtime_api.h>
+
+#include <cstdint>
+
+namespace mircuda_b200 {
+namespace w4a16_tile {
+
+struct Config {
+  int sm_count;
+  const void* cached_input;    // operands the tensor maps below were encoded for
+  const void* cached_weight;
+  CUtensorMap map_a, map_w;
+};
+
+// Shapes the kernel covers: n % 8 == 0 (16-byte output rows) and whole scale groups along K.
+bool eligible(int m, int n, int k);
+
+// Sets the kernel attribute and reads the device's SM count.
+int prepare(Config* config, int m, int n, int k);
+
+// input f16 [m, k], weight bytes [n, k / 2], scales f16 [n, k / 128], output f16 [m, n]; all
+// 16-byte aligned except the scales (2 bytes).
+int launch(Config* config, cudaStream_t stream, const void* input, const void* weight, const void* scales,
+           void* output, int m, int n, int k, uint32_t* status_word);
+
+}  // namespace w4a16_tile
+}  // namespace mircuda_b200

@@ -146,6 +146,27 @@ def test_w4a16_benchmark_shapes(cuda_stream, w4a16_kernel, m, n, k):
     assert_close(out, torch.from_numpy(expected.astype(np.float32)), f"w4a16 {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("prefill", ["tile", "expand"])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (40, 264, 384), (17, 8, 128), (300, 1000, 2176),
+                                   (128, 256, 128), (129, 776, 4096)])
+def test_w4a16_prefill_kernels(cuda_stream, monkeypatch, prefill, m, n, k):
+    """M > 16: the fused GEMM (packed weights expanded inside the kernel) and the two-launch form
+    (expansion into an f16 workspace, then the dense GEMM), ragged in M and N, one and many scale
+    groups along K; both must produce the oracle's product."""
+    monkeypatch.setenv("MIRCUDA_B200_W4A16_PREFILL", prefill)
+    from mircuda_b200 import dense
+    generator = torch.Generator(device="cuda").manual_seed(8300 + m)
+    weight = torch.randn(n, k, generator=generator, device="cuda") * 0.02
+    packed, scales = dense.quantize_int4(weight)
+    x = torch.randn(m, k, generator=generator, device="cuda").to(torch.float16)
+    out = run_w4a16(cuda_stream, x, packed, scales, m, n, k)
+    assert_w4a16_matches_oracle(out, x, packed, scales, f"w4a16 {prefill} {m}x{n}x{k}")
+    # other activations through a fresh plan (every plan runs twice: cached tensor maps)
+    x2 = torch.randn(m, k, generator=generator, device="cuda").to(torch.float16)
+    out2 = run_w4a16(cuda_stream, x2, packed, scales, m, n, k)
+    assert_w4a16_matches_oracle(out2, x2, packed, scales, f"w4a16 {prefill} {m}x{n}x{k} (second)")
+
+
 def test_w4a16_nibble_order(cuda_stream):
     """Only even-k codes differ from the zero point: exposes a swapped nibble order."""
     from mircuda_b200 import dense
