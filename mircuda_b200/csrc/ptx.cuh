@@ -102,13 +102,16 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 // orders of magnitude beyond any legitimate wait in these kernels.
 constexpr uint64_t kWaitBudgetNs = 500ull * 1000ull * 1000ull;
 
-template <uint64_t BUDGET_NS = kWaitBudgetNs>
+// PAUSE_NS > 0 puts the warp to sleep for about that long between polls: for roles that wait a
+// long time beside warps that compute (a tight poll loop takes issue slots from them).
+template <uint64_t BUDGET_NS = kWaitBudgetNs, uint32_t PAUSE_NS = 0>
 __device__ __forceinline__ bool mbarrier_wait(uint64_t* barrier, uint32_t parity,
                                               volatile uint32_t* abort) {
   if (mbarrier_try_wait(barrier, parity)) return true;
   const uint64_t start = global_timer_ns();
   for (uint32_t poll = 1;; ++poll) {
     if (mbarrier_try_wait(barrier, parity)) return true;
+    if constexpr (PAUSE_NS != 0u) __nanosleep(PAUSE_NS);
     if ((poll & 15u) == 0u) {
       if (*abort != 0u) return false;
       if (global_timer_ns() - start > BUDGET_NS) break;

@@ -359,6 +359,7 @@ struct Plan {
   w4a16_stream::Config stream_config;
   bool tile_kernel;          // the fused prefill GEMM of w4a16_tile.cu
   w4a16_tile::Config tile_config;
+  void* partial;             // its fp32 partial results when K is split
 };
 
 int parts_for(int n, int k, int slots, int max_parts) {
@@ -464,6 +465,9 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
         mircuda_b200::w4a16_tile::eligible(m, n, k)) {
       status = mircuda_b200::w4a16_tile::prepare(&plan->tile_config, m, n, k);
       plan->tile_kernel = status == 0;
+      if (status == 0 && plan->tile_config.workspace_bytes != 0u) {
+        status = static_cast<int>(cudaMallocAsync(&plan->partial, plan->tile_config.workspace_bytes, plan->stream));
+      }
     }
   }
   if (status == 0 && m > kVectorTokens && !plan->tile_kernel) {
@@ -477,6 +481,7 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
   if (status != 0) {
     if (plan->dense != nullptr) mircuda_dense_destroy(plan->dense);
     if (plan->expanded != nullptr) cudaFreeAsync(plan->expanded, plan->stream);
+    if (plan->partial != nullptr) cudaFreeAsync(plan->partial, plan->stream);
     if (plan->status != nullptr) cudaFreeHost(plan->status);
     delete plan;
     return status;
@@ -487,7 +492,9 @@ extern "C" int mircuda_b200_w4a16_create(int m, int n, int k, void* stream, void
 
 extern "C" size_t mircuda_b200_w4a16_workspace_bytes(const void* raw) {
   const auto* plan = static_cast<const mircuda_b200::w4a16::Plan*>(raw);
-  if (plan == nullptr || plan->expanded == nullptr) return 0;
+  if (plan == nullptr) return 0;
+  if (plan->tile_kernel) return plan->tile_config.workspace_bytes;
+  if (plan->expanded == nullptr) return 0;
   return static_cast<size_t>(plan->n) * plan->k * sizeof(__half);
 }
 
@@ -515,7 +522,7 @@ extern "C" int mircuda_b200_w4a16_execute(void* raw, void* stream, const void* i
   }
   if (plan->tile_kernel) {
     return mircuda_b200::w4a16_tile::launch(&plan->tile_config, cuda_stream, input, weight, scales, output,
-                                            plan->m, plan->n, plan->k, plan->status);
+                                            plan->partial, plan->m, plan->n, plan->k, plan->status);
   }
   if (plan->dense != nullptr) {
     const size_t words = static_cast<size_t>(plan->n) * plan->k / 8u;
@@ -552,6 +559,7 @@ extern "C" void mircuda_b200_w4a16_destroy(void* raw) {
   if (plan == nullptr) return;
   if (plan->dense != nullptr) mircuda_dense_destroy(plan->dense);
   if (plan->expanded != nullptr) cudaFreeAsync(plan->expanded, plan->stream);
+  if (plan->partial != nullptr) cudaFreeAsync(plan->partial, plan->stream);
   if (plan->status != nullptr) cudaFreeHost(plan->status);
   delete plan;
 }

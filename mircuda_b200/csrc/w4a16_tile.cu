@@ -5,17 +5,20 @@
 // reads and writes that workspace once more per call and took as long for the expansion as for
 // the GEMM.)
 //
-// One persistent 320-thread CTA per SM, tiles of 128 tokens x BN weight rows, 64 K-elements per
+// One persistent 448-thread CTA per SM, tiles of 128 tokens x BN weight rows, 64 K-elements per
 // stage:
 //  * warp 0 issues the TMA loads of a stage: the activation tile (128 rows x 128 bytes,
 //    128-byte swizzle) and the packed weight tile (BN rows x 32 bytes, no swizzle);
-//  * warps 6-9 (one thread per weight row, two rows for BN = 256) turn a row's 32 packed bytes
+//  * warps 6-13 (one thread per weight row) turn a row's 32 packed bytes
 //    into 64 f16 values (nibble OR-ed into the mantissa of 1024.0, minus 1032 = q - 8 exactly,
 //    times the group's f16 scale: the value the two-launch form stores) and write them as the
 //    K-major, 128-byte-swizzled B tile the tensor core reads: 16-byte piece c of row r goes to
 //    r * 128 + ((c ^ (r % 8)) * 16);
 //  * warp 1 issues four tcgen05.mma (kind::f16) per stage once both operands are in place;
 //  * warps 2-5 drain the accumulator (32 columns at a time) to f16 outputs.
+// When M and N give fewer tiles than half the SMs (M = 256 x N = 4096 is 32 tiles), K is cut
+// into `splits` ranges, a unit being (tile, range): the units store fp32 partial tiles into a
+// plan-owned workspace and a second small kernel adds the ranges in order and writes f16.
 // Every mbarrier wait is bounded; a wait that gives up raises the CTA's abort flag, every role
 // leaves its loop, tensor memory is freed and *status is set.
 #include <cuda.h>
@@ -35,20 +38,25 @@ namespace w4a16_tile {
 constexpr uint32_t kBlockM = 128;
 constexpr uint32_t kBlockK = 64;           // K-elements per stage: 128 bytes of f16, 32 of int4
 constexpr uint32_t kGroupK = 128;          // elements per scale group: two stages
-constexpr uint32_t kThreads = 320;
-constexpr uint32_t kConverterThreads = 128;
+constexpr uint32_t kConverterThreads = 256;
+constexpr uint32_t kThreads = 6u * 32u + kConverterThreads;   // 448
 constexpr uint32_t kTmemColumns = 512;
+constexpr uint32_t kChapterGroups = 32;    // scale groups of a row kept in shared memory at a time
 
-template <uint32_t BN, uint32_t STAGES>
+// STAGES: ring of loaded stages (activation tile + packed weight tile, 24 KB each at BN = 256),
+// deep enough to cover the latency of the loads; B_STAGES: ring of expanded weight tiles (32 KB
+// each), two being enough for the converters to work one stage ahead of the tensor core.
+template <uint32_t BN, uint32_t STAGES, uint32_t B_STAGES>
 struct Layout {
   static constexpr uint32_t kAccStages = 2;
   static constexpr uint32_t kABytes = kBlockM * 128u;
   static constexpr uint32_t kBBytes = BN * 128u;
   static constexpr uint32_t kPackedBytes = BN * 32u;
   static constexpr uint32_t kBOffset = STAGES * kABytes;
-  static constexpr uint32_t kPackedOffset = kBOffset + STAGES * kBBytes;
-  static constexpr uint32_t kBarrierOffset = kPackedOffset + STAGES * kPackedBytes;
-  static constexpr uint32_t kBarriers = 3 * STAGES + 2 * kAccStages;
+  static constexpr uint32_t kPackedOffset = kBOffset + B_STAGES * kBBytes;
+  static constexpr uint32_t kScaleOffset = kPackedOffset + STAGES * kPackedBytes;     // [group][row] f16
+  static constexpr uint32_t kBarrierOffset = kScaleOffset + kChapterGroups * BN * 2u;
+  static constexpr uint32_t kBarriers = 2 * STAGES + 2 * B_STAGES + 2 * kAccStages;
   static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
   static constexpr uint32_t kDynamicBytes = kMiscOffset + 16 + 1024;
   static_assert(kAccStages * BN <= kTmemColumns, "tensor memory budget");
@@ -94,18 +102,29 @@ __device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
   return v;
 }
 
+__device__ __forceinline__ uint32_t load_shared_u16(uint32_t address) {
+  uint32_t v;
+  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
+  return v;
+}
+
+__device__ __forceinline__ void store_shared_u16(uint32_t address, uint32_t v) {
+  asm volatile("st.shared.u16 [%0], %1;" ::"r"(address), "h"(static_cast<uint16_t>(v)) : "memory");
+}
+
 __device__ __forceinline__ void store_shared_16(uint32_t address, uint4 v) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z),
                "r"(v.w)
                : "memory");
 }
 
-template <uint32_t BN, uint32_t STAGES>
+template <uint32_t BN, uint32_t STAGES, uint32_t B_STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
 w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                  const __half* __restrict__ scales, __half* __restrict__ c, uint32_t m, uint32_t n,
-                  uint32_t k, uint32_t idesc, uint32_t* __restrict__ status) {
-  using L = Layout<BN, STAGES>;
+                  const __half* __restrict__ scales, __half* __restrict__ c, float* __restrict__ partial,
+                  uint32_t m, uint32_t n, uint32_t k, uint32_t splits, uint32_t idesc,
+                  uint32_t* __restrict__ status) {
+  using L = Layout<BN, STAGES, B_STAGES>;
   constexpr uint32_t kAccStages = L::kAccStages;
   extern __shared__ uint8_t dynamic_shared[];
   const uint32_t misalignment = ptx::smem_address(dynamic_shared) & 1023u;
@@ -114,9 +133,10 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* shared_b = shared + L::kBOffset;
   uint8_t* shared_packed = shared + L::kPackedOffset;
   uint64_t* loaded = reinterpret_cast<uint64_t*>(shared + L::kBarrierOffset);   // TMA -> converters
-  uint64_t* converted = loaded + STAGES;                                         // converters -> MMA
-  uint64_t* empty = converted + STAGES;                                          // MMA -> TMA
-  uint64_t* acc_full = empty + STAGES;
+  uint64_t* empty = loaded + STAGES;                                             // MMA -> TMA
+  uint64_t* converted = empty + STAGES;                                          // converters -> MMA
+  uint64_t* b_empty = converted + B_STAGES;                                      // MMA -> converters
+  uint64_t* acc_full = b_empty + B_STAGES;
   uint64_t* acc_empty = acc_full + kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(shared + L::kMiscOffset);
   volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
@@ -127,8 +147,11 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   if (threadIdx.x == 0) {
     for (uint32_t stage = 0; stage < STAGES; ++stage) {
       ptx::mbarrier_init(&loaded[stage], 1);
-      ptx::mbarrier_init(&converted[stage], kConverterThreads / 32u);
       ptx::mbarrier_init(&empty[stage], 1);
+    }
+    for (uint32_t stage = 0; stage < B_STAGES; ++stage) {
+      ptx::mbarrier_init(&converted[stage], kConverterThreads / 32u);
+      ptx::mbarrier_init(&b_empty[stage], 1);
     }
     for (uint32_t stage = 0; stage < kAccStages; ++stage) {
       ptx::mbarrier_init(&acc_full[stage], 1);
@@ -155,18 +178,21 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   const uint32_t tiles_m = (m + kBlockM - 1u) / kBlockM;
   const uint32_t tiles_n = (n + BN - 1u) / BN;
   const uint32_t tiles = tiles_m * tiles_n;
-  const uint32_t k_tiles = k / kBlockK;
+  const uint32_t units = tiles * splits;             // unit = tile + split * tiles
+  const uint32_t k_tiles = k / kBlockK / splits;     // per unit (an even number: whole scale groups)
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (ptx::elect_one()) {
       uint32_t stage = 0, phase = 0;
       bool running = true;
-      for (uint32_t tile = blockIdx.x; running && tile < tiles; tile += gridDim.x) {
+      for (uint32_t unit = blockIdx.x; running && unit < units; unit += gridDim.x) {
+        const uint32_t tile = unit % tiles;
+        const uint32_t first_kt = (unit / tiles) * k_tiles;
         const uint32_t m0 = (tile % tiles_m) * kBlockM;
         const uint32_t n0 = (tile / tiles_m) * BN;
-        for (uint32_t kt = 0; kt < k_tiles; ++kt) {
-          if (!ptx::mbarrier_wait(&empty[stage], phase ^ 1u, abort)) {
+        for (uint32_t kt = first_kt; kt < first_kt + k_tiles; ++kt) {
+          if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 64u>(&empty[stage], phase ^ 1u, abort)) {
             running = false;
             break;
           }
@@ -188,15 +214,15 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      uint32_t stage = 0, phase = 0, acc_stage = 0, acc_phase = 0;
+      uint32_t stage = 0, b_stage = 0, b_phase = 0, acc_stage = 0, acc_phase = 0;
       bool running = true;
-      for (uint32_t tile = blockIdx.x; running && tile < tiles; tile += gridDim.x) {
-        if (!ptx::mbarrier_wait(&acc_empty[acc_stage], acc_phase ^ 1u, abort)) break;
+      for (uint32_t unit = blockIdx.x; running && unit < units; unit += gridDim.x) {
+        if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 64u>(&acc_empty[acc_stage], acc_phase ^ 1u, abort)) break;
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc_stage * BN;
         for (uint32_t kt = 0; kt < k_tiles; ++kt) {
           // The converters arrive after the stage's loads have landed, so one wait covers both.
-          if (!ptx::mbarrier_wait(&converted[stage], phase, abort)) {
+          if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&converted[b_stage], b_phase, abort)) {
             running = false;
             break;
           }
@@ -204,15 +230,19 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           const uint64_t a_descriptor =
               ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_a + stage * L::kABytes));
           const uint64_t b_descriptor =
-              ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_b + stage * L::kBBytes));
+              ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_b + b_stage * L::kBBytes));
 #pragma unroll
           for (uint32_t kb = 0; kb < 4u; ++kb) {
             ptx::mma_f16(d_tmem, a_descriptor + 2u * kb, b_descriptor + 2u * kb, idesc, (kt | kb) != 0u);
           }
+          // These MMAs were the last readers of the stage's activation tile and of the expanded
+          // weight tile (its packed source was consumed before them).
           ptx::tcgen05_commit(&empty[stage]);
-          if (++stage == STAGES) {
-            stage = 0;
-            phase ^= 1u;
+          ptx::tcgen05_commit(&b_empty[b_stage]);
+          if (++stage == STAGES) stage = 0;
+          if (++b_stage == B_STAGES) {
+            b_stage = 0;
+            b_phase ^= 1u;
           }
         }
         if (!running) break;
@@ -227,10 +257,13 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     // ------------------------------------------------------------------ epilogue
     const uint32_t quarter = warp % 4u;
     uint32_t acc_stage = 0, acc_phase = 0;
-    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const uint32_t tile = unit % tiles;
       const uint32_t m0 = (tile % tiles_m) * kBlockM;
       const uint32_t n0 = (tile / tiles_m) * BN;
-      if (!ptx::mbarrier_wait(&acc_full[acc_stage], acc_phase, abort)) break;
+      float* partial_rows = partial + static_cast<size_t>(unit / tiles) * m * n;
+      // The epilogue warps wait for a whole tile's main loop beside the converters: sleep between polls.
+      if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 256u>(&acc_full[acc_stage], acc_phase, abort)) break;
       ptx::tcgen05_fence_after();
       const uint32_t row = m0 + quarter * 32u + lane;
       const uint32_t tmem_row = tmem_base + ((quarter * 32u) << 16) + acc_stage * BN;
@@ -240,7 +273,17 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         ptx::tmem_load_32x32(tmem_row + chunk * 32u, values);
         ptx::tmem_load_wait();
         const uint32_t column = n0 + chunk * 32u;
-        if (row < m && column < n) {
+        if (row < m && column < n && splits > 1u) {
+          // fp32 partial tile of this K range; n % 8 == 0 makes the pieces 16-byte aligned
+          float* destination = partial_rows + static_cast<size_t>(row) * n + column;
+#pragma unroll
+          for (uint32_t part = 0; part < 8u; ++part) {
+            if (column + part * 4u < n) {
+              reinterpret_cast<uint4*>(destination)[part] = make_uint4(values[part * 4u], values[part * 4u + 1u],
+                                                                      values[part * 4u + 2u], values[part * 4u + 3u]);
+            }
+          }
+        } else if (row < m && column < n) {
           __half* destination = c + static_cast<size_t>(row) * n + column;
           if (column + 32u <= n) {       // n % 8 == 0 and a 16-byte aligned base: 16-byte stores
 #pragma unroll
@@ -272,59 +315,73 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ converters
-    const uint32_t thread = threadIdx.x - 6u * 32u;          // 0..127
+    static_assert(BN == kConverterThreads, "one weight row per converter thread");
+    const uint32_t thread = threadIdx.x - 6u * 32u;          // 0..255 = row of the tile
     const uint32_t groups = k / kGroupK;
-    constexpr uint32_t kParts = BN / kConverterThreads;      // weight rows per thread
-    uint32_t stage = 0, phase = 0;
+    const uint32_t unit_groups = k_tiles / 2u;
+    // This row's scales of the next kChapterGroups groups live in shared memory, [group][row] so
+    // that a warp's reads are adjacent; every thread writes and reads only its own column, so
+    // no barrier is needed. (Global loads are kept out of the stage loop: the proxy fence at the
+    // end of a stage waits for every load the thread still has in flight.)
+    const uint32_t table = ptx::smem_address(shared + L::kScaleOffset) + thread * 2u;
+    uint32_t stage = 0, phase = 0, b_stage = 0, b_phase = 0;
     bool alive = true;
-    // The scale of a row's group is fetched one group ahead of its use (a group is two stages).
-    // Rows past N hold zero codes (TMA fill) and get a zero scale; nothing stores them.
-    auto fetch_scale = [&](uint32_t tile, uint32_t group, uint32_t part) -> uint32_t {
-      const uint32_t row = (tile / tiles_m) * BN + part * kConverterThreads + thread;
-      if (tile >= tiles || row >= n) return 0u;
-      return static_cast<uint32_t>(__half_as_ushort(__ldg(scales + static_cast<size_t>(row) * groups + group)));
-    };
-    uint32_t upcoming[kParts];
-#pragma unroll
-    for (uint32_t part = 0; part < kParts; ++part) upcoming[part] = fetch_scale(blockIdx.x, 0u, part);
-    for (uint32_t tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
-      uint32_t scale2[kParts] = {};
+    for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
+      const uint32_t row = ((unit % tiles) / tiles_m) * BN + thread;
+      const __half* row_scales = scales + static_cast<size_t>(row) * groups + (unit / tiles) * unit_groups;
+      uint32_t scale2 = 0u;
       for (uint32_t kt = 0; kt < k_tiles; ++kt) {
-        if ((kt & 1u) == 0u) {
-          const uint32_t group = kt / 2u;
+        if (kt % (2u * kChapterGroups) == 0u) {
+          // Rows past N hold zero codes (TMA fill) and get zero scales; nothing stores them.
+          const uint32_t first = kt / 2u;
+          const uint32_t count = min(kChapterGroups, unit_groups - first);
+          const __half* source = row_scales + first;
+          if (row < n && count % 8u == 0u && (reinterpret_cast<uintptr_t>(source) & 15u) == 0u) {
+            for (uint32_t group = 0; group < count; group += 8u) {
+              const uint4 eight = __ldg(reinterpret_cast<const uint4*>(source + group));
+              const uint32_t words[4] = {eight.x, eight.y, eight.z, eight.w};
 #pragma unroll
-          for (uint32_t part = 0; part < kParts; ++part) {
-            scale2[part] = upcoming[part] * 0x00010001u;
-            upcoming[part] = group + 1u < groups ? fetch_scale(tile, group + 1u, part)
-                                                 : fetch_scale(tile + gridDim.x, 0u, part);
+              for (uint32_t item = 0; item < 8u; ++item) {
+                store_shared_u16(table + (group + item) * (BN * 2u), words[item / 2u] >> (16u * (item % 2u)));
+              }
+            }
+          } else {
+            for (uint32_t group = 0; group < count; ++group) {
+              store_shared_u16(table + group * (BN * 2u),
+                               row < n ? static_cast<uint32_t>(__half_as_ushort(__ldg(source + group))) : 0u);
+            }
           }
+        }
+        if ((kt & 1u) == 0u) {
+          scale2 = load_shared_u16(table + ((kt / 2u) % kChapterGroups) * (BN * 2u)) * 0x00010001u;
         }
         // (Once a wait has run out, `abort` is raised and this thread skips every later wait: the
         // loops run to their end on meaningless data and the launch reports the failure.)
-        if (alive) alive = ptx::mbarrier_wait(&loaded[stage], phase, abort);
-        const uint32_t packed_base = ptx::smem_address(shared_packed + stage * L::kPackedBytes);
-        const uint32_t b_base = ptx::smem_address(shared_b + stage * L::kBBytes);
+        if (alive) alive = ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&loaded[stage], phase, abort);
+        if (alive) alive = ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&b_empty[b_stage], b_phase ^ 1u, abort);
+        ptx::tcgen05_fence_after();      // the MMAs that read this buffer are behind us
+        const uint32_t packed_row = ptx::smem_address(shared_packed + stage * L::kPackedBytes) + thread * 32u;
+        const uint32_t b_row = ptx::smem_address(shared_b + b_stage * L::kBBytes) + thread * 128u;
+        const uint4 low = load_shared_16(packed_row);
+        const uint4 high = load_shared_16(packed_row + 16u);
+        const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
+        const uint32_t swizzle = thread % 8u;
 #pragma unroll
-        for (uint32_t part = 0; part < kParts; ++part) {
-          const uint32_t row = part * kConverterThreads + thread;
-          const uint4 low = load_shared_16(packed_base + row * 32u);
-          const uint4 high = load_shared_16(packed_base + row * 32u + 16u);
-          const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
-          const uint32_t row_base = b_base + row * 128u;
-          const uint32_t swizzle = row % 8u;
-#pragma unroll
-          for (uint32_t piece = 0; piece < 8u; ++piece) {
-            store_shared_16(row_base + ((piece ^ swizzle) * 16u), expand8(words[piece], scale2[part]));
-          }
+        for (uint32_t piece = 0; piece < 8u; ++piece) {
+          store_shared_16(b_row + ((piece ^ swizzle) * 16u), expand8(words[piece], scale2));
         }
         // The tensor core reads shared memory through the async proxy: make this thread's
         // stores visible to it, then one arrival per warp.
         ptx::fence_proxy_async();
         __syncwarp();
-        if (lane == 0) ptx::mbarrier_arrive(&converted[stage]);
+        if (lane == 0) ptx::mbarrier_arrive(&converted[b_stage]);
         if (++stage == STAGES) {
           stage = 0;
           phase ^= 1u;
+        }
+        if (++b_stage == B_STAGES) {
+          b_stage = 0;
+          b_phase ^= 1u;
         }
       }
     }
@@ -340,8 +397,39 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   if (threadIdx.x == 0 && *abort != 0u) *status = 1u;
 }
 
+// Adds the K ranges' fp32 partial results in range order and writes f16; eight outputs a thread.
+__global__ void __launch_bounds__(256)
+w4a16_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ c, size_t vectors, uint32_t splits) {
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
+  for (size_t vector = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; vector < vectors;
+       vector += static_cast<size_t>(gridDim.x) * blockDim.x) {
+    float sums[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (uint32_t split = 0; split < splits; ++split) {
+      const float4* source = reinterpret_cast<const float4*>(partial) + (split * vectors + vector) * 2u;
+      const float4 low = __ldcs(source), high = __ldcs(source + 1);
+      sums[0] += low.x;
+      sums[1] += low.y;
+      sums[2] += low.z;
+      sums[3] += low.w;
+      sums[4] += high.x;
+      sums[5] += high.y;
+      sums[6] += high.z;
+      sums[7] += high.w;
+    }
+    uint32_t packed[4];
+#pragma unroll
+    for (int pair = 0; pair < 4; ++pair) {
+      const __half2 two = __floats2half2_rn(sums[2 * pair], sums[2 * pair + 1]);
+      packed[pair] = *reinterpret_cast<const uint32_t*>(&two);
+    }
+    reinterpret_cast<uint4*>(c)[vector] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
 constexpr uint32_t kBlockN = 256;
-constexpr uint32_t kStages = 4;
+constexpr uint32_t kStages = 6;
+constexpr uint32_t kBStages = 2;
 
 bool eligible(int m, int n, int k) { return m > 0 && n > 0 && n % 8 == 0 && k > 0 && k % kGroupK == 0; }
 
@@ -353,17 +441,35 @@ int prepare(Config* config, int m, int n, int k) {
     status = static_cast<int>(cudaDeviceGetAttribute(&config->sm_count, cudaDevAttrMultiProcessorCount, device));
   }
   if (status == 0) {
-    status = static_cast<int>(cudaFuncSetAttribute(w4a16_tile_kernel<kBlockN, kStages>,
+    status = static_cast<int>(cudaFuncSetAttribute(w4a16_tile_kernel<kBlockN, kStages, kBStages>,
                                                    cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                   Layout<kBlockN, kStages>::kDynamicBytes));
+                                                   Layout<kBlockN, kStages, kBStages>::kDynamicBytes));
   }
+  if (status != 0) return status;
+  // K ranges: as many as fill the SMs when the tiles alone leave more than half of them idle,
+  // each a whole number of scale groups (two stages) and at least eight groups long.
+  const int tiles = ((m + static_cast<int>(kBlockM) - 1) / static_cast<int>(kBlockM)) *
+                    ((n + static_cast<int>(kBlockN) - 1) / static_cast<int>(kBlockN));
+  const int groups = k / static_cast<int>(kGroupK);
+  int splits = 1;
+  if (tiles * 2 <= config->sm_count) {
+    for (int candidate = config->sm_count / tiles; candidate >= 2; --candidate) {
+      if (groups % candidate == 0 && groups / candidate >= 8) {
+        splits = candidate;
+        break;
+      }
+    }
+  }
+  config->splits = splits;
+  config->workspace_bytes = splits > 1 ? static_cast<size_t>(splits) * m * n * sizeof(float) : 0u;
   config->cached_input = nullptr;
   config->cached_weight = nullptr;
-  return status;
+  return 0;
 }
 
 int launch(Config* config, cudaStream_t stream, const void* input, const void* weight, const void* scales,
-           void* output, int m, int n, int k, uint32_t* status_word) {
+           void* output, void* workspace, int m, int n, int k, uint32_t* status_word) {
+  if (config->splits > 1 && workspace == nullptr) return -1;
   if (input != config->cached_input) {
     const int status = encode_k_major_map(&config->map_a, input, m, k, 2u, kBlockM);
     if (status != 0) return status;
@@ -384,15 +490,26 @@ int launch(Config* config, cudaStream_t stream, const void* input, const void* w
     if (status != 0) return status;
     config->cached_weight = weight;
   }
-  const uint32_t tiles = ((static_cast<uint32_t>(m) + kBlockM - 1u) / kBlockM) *
-                         ((static_cast<uint32_t>(n) + kBlockN - 1u) / kBlockN);
-  const uint32_t grid = tiles < static_cast<uint32_t>(config->sm_count) ? tiles : config->sm_count;
+  const uint32_t splits = static_cast<uint32_t>(config->splits);
+  const uint32_t units = ((static_cast<uint32_t>(m) + kBlockM - 1u) / kBlockM) *
+                         ((static_cast<uint32_t>(n) + kBlockN - 1u) / kBlockN) * splits;
+  const uint32_t grid = units < static_cast<uint32_t>(config->sm_count) ? units : config->sm_count;
   const uint32_t idesc = ptx::make_f16_idesc(false, kBlockM, kBlockN);
-  return launch_after_dependency(w4a16_tile_kernel<kBlockN, kStages>, dim3(grid), dim3(kThreads),
-                                 Layout<kBlockN, kStages>::kDynamicBytes, stream, config->map_a, config->map_w,
-                                 static_cast<const __half*>(scales), static_cast<__half*>(output),
-                                 static_cast<uint32_t>(m), static_cast<uint32_t>(n), static_cast<uint32_t>(k),
-                                 idesc, status_word);
+  int status = launch_after_dependency(w4a16_tile_kernel<kBlockN, kStages, kBStages>, dim3(grid), dim3(kThreads),
+                                       Layout<kBlockN, kStages, kBStages>::kDynamicBytes, stream, config->map_a,
+                                       config->map_w, static_cast<const __half*>(scales),
+                                       static_cast<__half*>(output), static_cast<float*>(workspace),
+                                       static_cast<uint32_t>(m), static_cast<uint32_t>(n),
+                                       static_cast<uint32_t>(k), splits, idesc, status_word);
+  if (status == 0 && splits > 1u) {
+    const size_t vectors = static_cast<size_t>(m) * n / 8u;
+    const size_t blocks = (vectors + 255u) / 256u;
+    status = launch_after_dependency(w4a16_reduce_kernel,
+                                     dim3(static_cast<unsigned int>(blocks < 148u * 16u ? blocks : 148u * 16u)),
+                                     dim3(256), 0, stream, static_cast<const float*>(workspace),
+                                     static_cast<__half*>(output), vectors, splits);
+  }
+  return status;
 }
 
 }  // namespace w4a16_tile

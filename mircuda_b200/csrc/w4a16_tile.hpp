@@ -12,6 +12,8 @@ namespace w4a16_tile {
 
 struct Config {
   int sm_count;
+  int splits;                  // K ranges per tile; more than one needs the workspace
+  size_t workspace_bytes;      // splits * m * n floats when splits > 1, else 0
   const void* cached_input;    // operands the tensor maps below were encoded for
   const void* cached_weight;
   CUtensorMap map_a, map_w;
@@ -20,13 +22,13 @@ struct Config {
 // Shapes the kernel covers: n % 8 == 0 (16-byte output rows) and whole scale groups along K.
 bool eligible(int m, int n, int k);
 
-// Sets the kernel attribute and reads the device's SM count.
+// Sets the kernel attribute, reads the device's SM count and decides the K split.
 int prepare(Config* config, int m, int n, int k);
 
 // input f16 [m, k], weight bytes [n, k / 2], scales f16 [n, k / 128], output f16 [m, n]; all
-// 16-byte aligned except the scales (2 bytes).
+// 16-byte aligned except the scales (2 bytes). `workspace`: workspace_bytes of device memory.
 int launch(Config* config, cudaStream_t stream, const void* input, const void* weight, const void* scales,
-           void* output, int m, int n, int k, uint32_t* status_word);
+           void* output, void* workspace, int m, int n, int k, uint32_t* status_word);
 
 }  // namespace w4a16_tile
 }  // namespace mircuda_b200
