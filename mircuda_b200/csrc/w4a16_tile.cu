@@ -7,9 +7,11 @@
 //
 // One persistent 448-thread CTA per SM, tiles of 128 tokens x BN weight rows, 64 K-elements per
 // stage:
-//  * warp 0 issues the TMA loads of a stage: the activation tile (128 rows x 128 bytes,
-//    128-byte swizzle) and the packed weight tile (BN rows x 32 bytes, no swizzle);
-//  * warps 6-13 (one thread per weight row) turn a row's 32 packed bytes
+//  * warp 0 issues the TMA loads: per stage the activation tile (128 rows x 128 bytes, 128-byte
+//    swizzle), and once per two stages the packed weight rows of those stages (BN rows x 64
+//    bytes);
+//  * warps 6-13 (two groups of four taking the stages in turn, two weight rows per thread) turn a
+//    row's 32 packed bytes
 //    into 64 f16 values (nibble OR-ed into the mantissa of 1024.0, minus 1032 = q - 8 exactly,
 //    times the group's f16 scale: the value the two-launch form stores) and write them as the
 //    K-major, 128-byte-swizzled B tile the tensor core reads: 16-byte piece c of row r goes to
@@ -41,22 +43,29 @@ constexpr uint32_t kGroupK = 128;          // elements per scale group: two stag
 constexpr uint32_t kConverterThreads = 256;
 constexpr uint32_t kThreads = 6u * 32u + kConverterThreads;   // 448
 constexpr uint32_t kTmemColumns = 512;
-constexpr uint32_t kChapterGroups = 32;    // scale groups of a row kept in shared memory at a time
+constexpr uint32_t kChapterGroups = 16;    // scale groups of a row kept in shared memory at a time
+constexpr uint32_t kConverterGroups = 2;   // groups of converter warps, taking the stages in turn
+constexpr uint32_t kGroupThreads = kConverterThreads / kConverterGroups;   // 128
 
-// STAGES: ring of loaded stages (activation tile + packed weight tile, 24 KB each at BN = 256),
-// deep enough to cover the latency of the loads; B_STAGES: ring of expanded weight tiles (32 KB
-// each), two being enough for the converters to work one stage ahead of the tensor core.
+// STAGES: ring of activation tiles (16 KB each), deep enough to cover the latency of the loads;
+// B_STAGES: ring of expanded weight tiles (32 KB each at BN = 256): with two, a tile could only
+// be expanded after the MMAs two stages back had finished and the hand-over latencies added up
+// to a stage period of twice the MMA time; three let the converters run ahead. kPackedStages:
+// ring of packed weight tiles, each the rows' bytes of two stages (16 KB).
+constexpr uint32_t kPackedStages = 2;
+constexpr uint32_t kQuad = 2;              // stages covered by one packed tile
+
 template <uint32_t BN, uint32_t STAGES, uint32_t B_STAGES>
 struct Layout {
   static constexpr uint32_t kAccStages = 2;
   static constexpr uint32_t kABytes = kBlockM * 128u;
   static constexpr uint32_t kBBytes = BN * 128u;
-  static constexpr uint32_t kPackedBytes = BN * 32u;
+  static constexpr uint32_t kPackedBytes = BN * 32u * kQuad;
   static constexpr uint32_t kBOffset = STAGES * kABytes;
   static constexpr uint32_t kPackedOffset = kBOffset + B_STAGES * kBBytes;
-  static constexpr uint32_t kScaleOffset = kPackedOffset + STAGES * kPackedBytes;     // [group][row] f16
-  static constexpr uint32_t kBarrierOffset = kScaleOffset + kChapterGroups * BN * 2u;
-  static constexpr uint32_t kBarriers = 2 * STAGES + 2 * B_STAGES + 2 * kAccStages;
+  static constexpr uint32_t kScaleOffset = kPackedOffset + kPackedStages * kPackedBytes;   // [group][row] f16
+  static constexpr uint32_t kBarrierOffset = kScaleOffset + kConverterGroups * kChapterGroups * BN * 2u;
+  static constexpr uint32_t kBarriers = 2 * STAGES + 2 * B_STAGES + 2 * kPackedStages + 2 * kAccStages;
   static constexpr uint32_t kMiscOffset = kBarrierOffset + kBarriers * 8;
   static constexpr uint32_t kDynamicBytes = kMiscOffset + 16 + 1024;
   static_assert(kAccStages * BN <= kTmemColumns, "tensor memory budget");
@@ -132,11 +141,13 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   uint8_t* shared_a = shared;
   uint8_t* shared_b = shared + L::kBOffset;
   uint8_t* shared_packed = shared + L::kPackedOffset;
-  uint64_t* loaded = reinterpret_cast<uint64_t*>(shared + L::kBarrierOffset);   // TMA -> converters
+  uint64_t* loaded = reinterpret_cast<uint64_t*>(shared + L::kBarrierOffset);   // TMA -> MMA (activations)
   uint64_t* empty = loaded + STAGES;                                             // MMA -> TMA
   uint64_t* converted = empty + STAGES;                                          // converters -> MMA
   uint64_t* b_empty = converted + B_STAGES;                                      // MMA -> converters
-  uint64_t* acc_full = b_empty + B_STAGES;
+  uint64_t* packed_full = b_empty + B_STAGES;                                    // TMA -> converters
+  uint64_t* packed_empty = packed_full + kPackedStages;                          // converters -> TMA
+  uint64_t* acc_full = packed_empty + kPackedStages;
   uint64_t* acc_empty = acc_full + kAccStages;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(shared + L::kMiscOffset);
   volatile uint32_t* abort = reinterpret_cast<volatile uint32_t*>(tmem_slot + 1);
@@ -150,8 +161,12 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
       ptx::mbarrier_init(&empty[stage], 1);
     }
     for (uint32_t stage = 0; stage < B_STAGES; ++stage) {
-      ptx::mbarrier_init(&converted[stage], kConverterThreads / 32u);
+      ptx::mbarrier_init(&converted[stage], kGroupThreads / 32u);
       ptx::mbarrier_init(&b_empty[stage], 1);
+    }
+    for (uint32_t stage = 0; stage < kPackedStages; ++stage) {
+      ptx::mbarrier_init(&packed_full[stage], 1);
+      ptx::mbarrier_init(&packed_empty[stage], kConverterThreads / 32u);
     }
     for (uint32_t stage = 0; stage < kAccStages; ++stage) {
       ptx::mbarrier_init(&acc_full[stage], 1);
@@ -184,7 +199,7 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (ptx::elect_one()) {
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, packed_stage = 0, packed_phase = 0;
       bool running = true;
       for (uint32_t unit = blockIdx.x; running && unit < units; unit += gridDim.x) {
         const uint32_t tile = unit % tiles;
@@ -192,15 +207,27 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
         const uint32_t m0 = (tile % tiles_m) * kBlockM;
         const uint32_t n0 = (tile / tiles_m) * BN;
         for (uint32_t kt = first_kt; kt < first_kt + k_tiles; ++kt) {
+          if ((kt - first_kt) % kQuad == 0u) {
+            // The packed bytes of the next two stages.
+            if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 64u>(&packed_empty[packed_stage], packed_phase ^ 1u, abort)) {
+              running = false;
+              break;
+            }
+            ptx::mbarrier_arrive_expect_tx(&packed_full[packed_stage], L::kPackedBytes);
+            ptx::tma_load_2d(shared_packed + packed_stage * L::kPackedBytes, &map_w, &packed_full[packed_stage],
+                             static_cast<int32_t>(kt * (kBlockK / 2u)), static_cast<int32_t>(n0));
+            if (++packed_stage == kPackedStages) {
+              packed_stage = 0;
+              packed_phase ^= 1u;
+            }
+          }
           if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 64u>(&empty[stage], phase ^ 1u, abort)) {
             running = false;
             break;
           }
-          ptx::mbarrier_arrive_expect_tx(&loaded[stage], L::kABytes + L::kPackedBytes);
+          ptx::mbarrier_arrive_expect_tx(&loaded[stage], L::kABytes);
           ptx::tma_load_2d(shared_a + stage * L::kABytes, &map_a, &loaded[stage],
                            static_cast<int32_t>(kt * kBlockK), static_cast<int32_t>(m0));
-          ptx::tma_load_2d(shared_packed + stage * L::kPackedBytes, &map_w, &loaded[stage],
-                           static_cast<int32_t>(kt * (kBlockK / 2u)), static_cast<int32_t>(n0));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -214,15 +241,15 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer
     if (ptx::elect_one()) {
-      uint32_t stage = 0, b_stage = 0, b_phase = 0, acc_stage = 0, acc_phase = 0;
+      uint32_t stage = 0, phase = 0, b_stage = 0, b_phase = 0, acc_stage = 0, acc_phase = 0;
       bool running = true;
       for (uint32_t unit = blockIdx.x; running && unit < units; unit += gridDim.x) {
         if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 64u>(&acc_empty[acc_stage], acc_phase ^ 1u, abort)) break;
         ptx::tcgen05_fence_after();
         const uint32_t d_tmem = tmem_base + acc_stage * BN;
         for (uint32_t kt = 0; kt < k_tiles; ++kt) {
-          // The converters arrive after the stage's loads have landed, so one wait covers both.
-          if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&converted[b_stage], b_phase, abort)) {
+          if (!ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&loaded[stage], phase, abort) ||
+              !ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&converted[b_stage], b_phase, abort)) {
             running = false;
             break;
           }
@@ -239,7 +266,10 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
           // weight tile (its packed source was consumed before them).
           ptx::tcgen05_commit(&empty[stage]);
           ptx::tcgen05_commit(&b_empty[b_stage]);
-          if (++stage == STAGES) stage = 0;
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
           if (++b_stage == B_STAGES) {
             b_stage = 0;
             b_phase ^= 1u;
@@ -315,72 +345,95 @@ w4a16_tile_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
     }
   } else {
     // ------------------------------------------------------------------ converters
-    static_assert(BN == kConverterThreads, "one weight row per converter thread");
-    const uint32_t thread = threadIdx.x - 6u * 32u;          // 0..255 = row of the tile
-    const uint32_t groups = k / kGroupK;
+    // Two groups of four warps take the stages in turn (group g the stages with kt % 2 == g, a
+    // thread the rows t and t + 128 of the tile), so that two stages are being expanded at any
+    // time: one stage's expansion is a chain of shared-memory loads, arithmetic, stores and a
+    // proxy fence about as long as two stages of MMAs, and a single group working stage after
+    // stage held the tensor pipe at a third of its rate.
+    static_assert(BN == 2u * kGroupThreads, "two weight rows per converter thread");
+    static_assert(kQuad == kConverterGroups, "every group takes one stage of a packed tile");
+    const uint32_t group = (threadIdx.x - 6u * 32u) / kGroupThreads;
+    const uint32_t thread = (threadIdx.x - 6u * 32u) % kGroupThreads;
+    const uint32_t groups_k = k / kGroupK;
     const uint32_t unit_groups = k_tiles / 2u;
-    // This row's scales of the next kChapterGroups groups live in shared memory, [group][row] so
-    // that a warp's reads are adjacent; every thread writes and reads only its own column, so
-    // no barrier is needed. (Global loads are kept out of the stage loop: the proxy fence at the
-    // end of a stage waits for every load the thread still has in flight.)
-    const uint32_t table = ptx::smem_address(shared + L::kScaleOffset) + thread * 2u;
-    uint32_t stage = 0, phase = 0, b_stage = 0, b_phase = 0;
+    // The rows' scales of the next kChapterGroups scale groups live in shared memory, one table
+    // per converter group, [scale group][row] so that a warp's reads are adjacent; a thread
+    // writes and reads only its own two columns, so no barrier is needed. (Global loads are kept
+    // out of the stage loop: the proxy fence at the end of a stage waits for every load the
+    // thread still has in flight.)
+    const uint32_t table = ptx::smem_address(shared + L::kScaleOffset) + group * (kChapterGroups * BN * 2u) +
+                           thread * 2u;
+    // Ring positions advance with every stage, also the other group's.
+    uint32_t packed_stage = 0, packed_phase = 0, b_stage = group % B_STAGES, b_phase = 0;
     bool alive = true;
     for (uint32_t unit = blockIdx.x; unit < units; unit += gridDim.x) {
-      const uint32_t row = ((unit % tiles) / tiles_m) * BN + thread;
-      const __half* row_scales = scales + static_cast<size_t>(row) * groups + (unit / tiles) * unit_groups;
-      uint32_t scale2 = 0u;
-      for (uint32_t kt = 0; kt < k_tiles; ++kt) {
-        if (kt % (2u * kChapterGroups) == 0u) {
+      const uint32_t first_row = ((unit % tiles) / tiles_m) * BN + thread;
+      const __half* unit_scales = scales + (unit / tiles) * unit_groups;
+      for (uint32_t kt = group; kt < k_tiles; kt += kConverterGroups) {
+        const uint32_t scale_group = kt / 2u;
+        if (scale_group % kChapterGroups == 0u) {
           // Rows past N hold zero codes (TMA fill) and get zero scales; nothing stores them.
-          const uint32_t first = kt / 2u;
-          const uint32_t count = min(kChapterGroups, unit_groups - first);
-          const __half* source = row_scales + first;
-          if (row < n && count % 8u == 0u && (reinterpret_cast<uintptr_t>(source) & 15u) == 0u) {
-            for (uint32_t group = 0; group < count; group += 8u) {
-              const uint4 eight = __ldg(reinterpret_cast<const uint4*>(source + group));
-              const uint32_t words[4] = {eight.x, eight.y, eight.z, eight.w};
+          const uint32_t count = min(kChapterGroups, unit_groups - scale_group);
 #pragma unroll
-              for (uint32_t item = 0; item < 8u; ++item) {
-                store_shared_u16(table + (group + item) * (BN * 2u), words[item / 2u] >> (16u * (item % 2u)));
+          for (uint32_t part = 0; part < 2u; ++part) {
+            const uint32_t row = first_row + part * kGroupThreads;
+            const __half* source = unit_scales + static_cast<size_t>(row) * groups_k + scale_group;
+            const uint32_t column = table + part * (kGroupThreads * 2u);
+            if (row < n && count % 8u == 0u && (reinterpret_cast<uintptr_t>(source) & 15u) == 0u) {
+              for (uint32_t item_group = 0; item_group < count; item_group += 8u) {
+                const uint4 eight = __ldg(reinterpret_cast<const uint4*>(source + item_group));
+                const uint32_t words[4] = {eight.x, eight.y, eight.z, eight.w};
+#pragma unroll
+                for (uint32_t item = 0; item < 8u; ++item) {
+                  store_shared_u16(column + (item_group + item) * (BN * 2u), words[item / 2u] >> (16u * (item % 2u)));
+                }
               }
-            }
-          } else {
-            for (uint32_t group = 0; group < count; ++group) {
-              store_shared_u16(table + group * (BN * 2u),
-                               row < n ? static_cast<uint32_t>(__half_as_ushort(__ldg(source + group))) : 0u);
+            } else {
+              for (uint32_t item = 0; item < count; ++item) {
+                store_shared_u16(column + item * (BN * 2u),
+                                 row < n ? static_cast<uint32_t>(__half_as_ushort(__ldg(source + item))) : 0u);
+              }
             }
           }
         }
-        if ((kt & 1u) == 0u) {
-          scale2 = load_shared_u16(table + ((kt / 2u) % kChapterGroups) * (BN * 2u)) * 0x00010001u;
-        }
         // (Once a wait has run out, `abort` is raised and this thread skips every later wait: the
         // loops run to their end on meaningless data and the launch reports the failure.)
-        if (alive) alive = ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&loaded[stage], phase, abort);
+        if (alive) alive = ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&packed_full[packed_stage], packed_phase, abort);
         if (alive) alive = ptx::mbarrier_wait<ptx::kWaitBudgetNs, 32u>(&b_empty[b_stage], b_phase ^ 1u, abort);
         ptx::tcgen05_fence_after();      // the MMAs that read this buffer are behind us
-        const uint32_t packed_row = ptx::smem_address(shared_packed + stage * L::kPackedBytes) + thread * 32u;
-        const uint32_t b_row = ptx::smem_address(shared_b + b_stage * L::kBBytes) + thread * 128u;
-        const uint4 low = load_shared_16(packed_row);
-        const uint4 high = load_shared_16(packed_row + 16u);
-        const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
-        const uint32_t swizzle = thread % 8u;
+        // This group's 32 bytes of a row's 64 in the packed tile (not swizzled).
+        const uint32_t packed_tile = ptx::smem_address(shared_packed + packed_stage * L::kPackedBytes) + group * 32u;
+        const uint32_t b_tile = ptx::smem_address(shared_b + b_stage * L::kBBytes);
+        const uint32_t swizzle = thread % 8u;     // the same for both rows (128 apart)
 #pragma unroll
-        for (uint32_t piece = 0; piece < 8u; ++piece) {
-          store_shared_16(b_row + ((piece ^ swizzle) * 16u), expand8(words[piece], scale2));
+        for (uint32_t part = 0; part < 2u; ++part) {
+          const uint32_t row = thread + part * kGroupThreads;
+          const uint32_t scale2 = load_shared_u16(table + part * (kGroupThreads * 2u) +
+                                                  (scale_group % kChapterGroups) * (BN * 2u)) * 0x00010001u;
+          const uint4 low = load_shared_16(packed_tile + row * 64u);
+          const uint4 high = load_shared_16(packed_tile + row * 64u + 16u);
+          const uint32_t words[8] = {low.x, low.y, low.z, low.w, high.x, high.y, high.z, high.w};
+#pragma unroll
+          for (uint32_t piece = 0; piece < 8u; ++piece) {
+            store_shared_16(b_tile + row * 128u + ((piece ^ swizzle) * 16u), expand8(words[piece], scale2));
+          }
         }
         // The tensor core reads shared memory through the async proxy: make this thread's
         // stores visible to it, then one arrival per warp.
         ptx::fence_proxy_async();
         __syncwarp();
         if (lane == 0) ptx::mbarrier_arrive(&converted[b_stage]);
-        if (++stage == STAGES) {
-          stage = 0;
-          phase ^= 1u;
+        // This warp is done with the packed tile (its reads returned before the stores that used
+        // them were issued).
+        if (lane == 0) ptx::mbarrier_arrive(&packed_empty[packed_stage]);
+        if (++packed_stage == kPackedStages) {
+          packed_stage = 0;
+          packed_phase ^= 1u;
         }
-        if (++b_stage == B_STAGES) {
-          b_stage = 0;
+        // two stages on in the ring of expanded tiles
+        b_stage += kConverterGroups;
+        if (b_stage >= B_STAGES) {
+          b_stage -= B_STAGES;
           b_phase ^= 1u;
         }
       }
@@ -428,8 +481,8 @@ w4a16_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ c, s
 }
 
 constexpr uint32_t kBlockN = 256;
-constexpr uint32_t kStages = 6;
-constexpr uint32_t kBStages = 2;
+constexpr uint32_t kStages = 4;
+constexpr uint32_t kBStages = 3;
 
 bool eligible(int m, int n, int k) { return m > 0 && n > 0 && n % 8 == 0 && k > 0 && k % kGroupK == 0; }
 
@@ -476,12 +529,12 @@ int launch(Config* config, cudaStream_t stream, const void* input, const void* w
     config->cached_input = input;
   }
   if (weight != config->cached_weight) {
-    // Packed weights as bytes [N, K / 2]; a box is 32 bytes (64 codes) of BN rows, not swizzled.
+    // Packed weights as bytes [N, K / 2]; a box is 64 bytes (two stages' codes) of BN rows.
     EncodeTiled encode = encode_tiled_entry();
     if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
     const cuuint64_t dimensions[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
-    const cuuint32_t box[2] = {kBlockK / 2u, kBlockN};
+    const cuuint32_t box[2] = {kQuad * kBlockK / 2u, kBlockN};
     const cuuint32_t element_strides[2] = {1u, 1u};
     const int status = static_cast<int>(encode(
         &config->map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2u, const_cast<void*>(weight), dimensions, strides, box,
