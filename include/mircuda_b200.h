@@ -420,8 +420,11 @@ void mircuda_dense_destroy(void* plan);
  * NEW: the reference's W4A16 is the NVFP4/MXFP4 Marlin path; it has no int4 entry point.
  * y[m, n] = f16(sum_k x[m, k] * (q[n, k] - 8) * s[n, k / 128]): x, y f16; weights [n, k/2]
  * bytes, even k in the low nibble, q in 0..15; scales f16 [n, k/128]. k % 128 == 0,
- * n % 8 == 0. m <= 16 streams the packed weights once (HBM-bound GEMV); larger m expands the
- * weights into a plan-owned f16 workspace (workspace_bytes) and runs the dense GEMM. At m <= 16
+ * n % 8 == 0. m <= 16 streams the packed weights once (HBM-bound GEMV); larger m runs a tcgen05
+ * GEMM that expands the packed weights inside the kernel (the plan owns fp32 partial sums,
+ * workspace_bytes, only where it splits K because m and n give few tiles;
+ * MIRCUDA_B200_W4A16_PREFILL=expand selects the older form: expansion into a plan-owned f16
+ * workspace of n * k halves, then the dense GEMM). At m <= 16
  * with n % 16 == 0 and k % 2048 == 0 (the streaming kernel; `scales` must then be 4-byte
  * aligned) launches overlap as described for mircuda_b200_nvfp4_vector_*: weights and scales
  * are fetched while earlier work of the stream may still run. */
