@@ -481,7 +481,7 @@ w4a16_reduce_kernel(const float* __restrict__ partial, __half* __restrict__ c, s
 }
 
 constexpr uint32_t kBlockN = 256;
-constexpr uint32_t kStages = 4;
+constexpr uint32_t kStages = 5;
 constexpr uint32_t kBStages = 3;
 
 bool eligible(int m, int n, int k) { return m > 0 && n > 0 && n % 8 == 0 && k > 0 && k % kGroupK == 0; }
