@@ -28,10 +28,13 @@
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
+#include <cstdlib>
+#include <cstring>
 
 #include "launch_overlap.hpp"
 #include "ptx.cuh"
 #include "tensor_map.hpp"
+#include "w4a16_expand.cuh"
 #include "w4a16_tile.hpp"
 
 namespace mircuda_b200 {
@@ -72,60 +75,7 @@ struct Layout {
   static_assert(kDynamicBytes <= 232448, "shared memory budget");
 };
 
-__device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t selector) {
-  uint32_t d;
-  asm("prmt.b32 %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(selector));
-  return d;
-}
-
-__device__ __forceinline__ uint32_t sub_f16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-__device__ __forceinline__ uint32_t mul_f16x2(uint32_t a, uint32_t b) {
-  uint32_t d;
-  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
-  return d;
-}
-
-// Eight codes of one word (k ascending from the low nibble) -> (q - 8) * scale as four f16x2 in
-// K order. 0x6400 is 1024.0 in f16: OR-ing a nibble into its mantissa gives 1024 + q exactly.
-__device__ __forceinline__ uint4 expand8(uint32_t codes, uint32_t scale2) {
-  constexpr uint32_t kMask = 0x000f000fu, kMagic = 0x64006400u, kBias = 0x64086408u;   // 1032.0
-  const uint32_t v04 = mul_f16x2(sub_f16x2((codes & kMask) | kMagic, kBias), scale2);           // k0, k4
-  const uint32_t v15 = mul_f16x2(sub_f16x2(((codes >> 4) & kMask) | kMagic, kBias), scale2);    // k1, k5
-  const uint32_t v26 = mul_f16x2(sub_f16x2(((codes >> 8) & kMask) | kMagic, kBias), scale2);    // k2, k6
-  const uint32_t v37 = mul_f16x2(sub_f16x2(((codes >> 12) & kMask) | kMagic, kBias), scale2);   // k3, k7
-  return make_uint4(prmt(v04, v15, 0x5410u), prmt(v26, v37, 0x5410u), prmt(v04, v15, 0x7632u),
-                    prmt(v26, v37, 0x7632u));
-}
-
-__device__ __forceinline__ uint4 load_shared_16(uint32_t address) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
-               : "r"(address)
-               : "memory");
-  return v;
-}
-
-__device__ __forceinline__ uint32_t load_shared_u16(uint32_t address) {
-  uint32_t v;
-  asm volatile("ld.shared.u16 %0, [%1];" : "=r"(v) : "r"(address) : "memory");
-  return v;
-}
-
-__device__ __forceinline__ void store_shared_u16(uint32_t address, uint32_t v) {
-  asm volatile("st.shared.u16 [%0], %1;" ::"r"(address), "h"(static_cast<uint16_t>(v)) : "memory");
-}
-
-__device__ __forceinline__ void store_shared_16(uint32_t address, uint4 v) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(address), "r"(v.x), "r"(v.y), "r"(v.z),
-               "r"(v.w)
-               : "memory");
-}
+using namespace w4a16_expand;
 
 template <uint32_t BN, uint32_t STAGES, uint32_t B_STAGES>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -499,14 +449,24 @@ int prepare(Config* config, int m, int n, int k) {
                                                    Layout<kBlockN, kStages, kBStages>::kDynamicBytes));
   }
   if (status != 0) return status;
+  // More than 128 tokens run on CTA pairs (tiles of 256 tokens; MIRCUDA_B200_W4A16_PREFILL=single
+  // keeps single CTAs).
+  const char* choice = std::getenv("MIRCUDA_B200_W4A16_PREFILL");
+  config->pair = m > static_cast<int>(kBlockM) && !(choice != nullptr && std::strcmp(choice, "single") == 0);
+  config->resident_pairs = 0;
+  if (config->pair) {
+    status = prepare_pair(config);
+    if (status != 0) return status;
+  }
   // K ranges: as many as fill the SMs when the tiles alone leave more than half of them idle,
   // each a whole number of scale groups (two stages) and at least eight groups long.
-  const int tiles = ((m + static_cast<int>(kBlockM) - 1) / static_cast<int>(kBlockM)) *
-                    ((n + static_cast<int>(kBlockN) - 1) / static_cast<int>(kBlockN));
+  const int tile_m = static_cast<int>(kBlockM) * (config->pair ? 2 : 1);
+  const int slots = config->pair ? config->resident_pairs : config->sm_count;
+  const int tiles = ((m + tile_m - 1) / tile_m) * ((n + static_cast<int>(kBlockN) - 1) / static_cast<int>(kBlockN));
   const int groups = k / static_cast<int>(kGroupK);
   int splits = 1;
-  if (tiles * 2 <= config->sm_count) {
-    for (int candidate = config->sm_count / tiles; candidate >= 2; --candidate) {
+  if (tiles * 2 <= slots) {
+    for (int candidate = slots / tiles; candidate >= 2; --candidate) {
       if (groups % candidate == 0 && groups / candidate >= 8) {
         splits = candidate;
         break;
@@ -534,7 +494,7 @@ int launch(Config* config, cudaStream_t stream, const void* input, const void* w
     if (encode == nullptr) return static_cast<int>(cudaErrorNotSupported);
     const cuuint64_t dimensions[2] = {static_cast<cuuint64_t>(k / 2), static_cast<cuuint64_t>(n)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(k / 2)};
-    const cuuint32_t box[2] = {kQuad * kBlockK / 2u, kBlockN};
+    const cuuint32_t box[2] = {kQuad * kBlockK / 2u, config->pair ? kBlockN / 2u : kBlockN};
     const cuuint32_t element_strides[2] = {1u, 1u};
     const int status = static_cast<int>(encode(
         &config->map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2u, const_cast<void*>(weight), dimensions, strides, box,
@@ -544,16 +504,21 @@ int launch(Config* config, cudaStream_t stream, const void* input, const void* w
     config->cached_weight = weight;
   }
   const uint32_t splits = static_cast<uint32_t>(config->splits);
-  const uint32_t units = ((static_cast<uint32_t>(m) + kBlockM - 1u) / kBlockM) *
-                         ((static_cast<uint32_t>(n) + kBlockN - 1u) / kBlockN) * splits;
-  const uint32_t grid = units < static_cast<uint32_t>(config->sm_count) ? units : config->sm_count;
-  const uint32_t idesc = ptx::make_f16_idesc(false, kBlockM, kBlockN);
-  int status = launch_after_dependency(w4a16_tile_kernel<kBlockN, kStages, kBStages>, dim3(grid), dim3(kThreads),
-                                       Layout<kBlockN, kStages, kBStages>::kDynamicBytes, stream, config->map_a,
-                                       config->map_w, static_cast<const __half*>(scales),
-                                       static_cast<__half*>(output), static_cast<float*>(workspace),
-                                       static_cast<uint32_t>(m), static_cast<uint32_t>(n),
-                                       static_cast<uint32_t>(k), splits, idesc, status_word);
+  int status = 0;
+  if (config->pair) {
+    status = launch_pair(config, stream, scales, output, workspace, m, n, k, status_word);
+  } else {
+    const uint32_t units = ((static_cast<uint32_t>(m) + kBlockM - 1u) / kBlockM) *
+                           ((static_cast<uint32_t>(n) + kBlockN - 1u) / kBlockN) * splits;
+    const uint32_t grid = units < static_cast<uint32_t>(config->sm_count) ? units : config->sm_count;
+    const uint32_t idesc = ptx::make_f16_idesc(false, kBlockM, kBlockN);
+    status = launch_after_dependency(w4a16_tile_kernel<kBlockN, kStages, kBStages>, dim3(grid), dim3(kThreads),
+                                     Layout<kBlockN, kStages, kBStages>::kDynamicBytes, stream, config->map_a,
+                                     config->map_w, static_cast<const __half*>(scales),
+                                     static_cast<__half*>(output), static_cast<float*>(workspace),
+                                     static_cast<uint32_t>(m), static_cast<uint32_t>(n),
+                                     static_cast<uint32_t>(k), splits, idesc, status_word);
+  }
   if (status == 0 && splits > 1u) {
     const size_t vectors = static_cast<size_t>(m) * n / 8u;
     const size_t blocks = (vectors + 255u) / 256u;

@@ -11,6 +11,8 @@ namespace mircuda_b200 {
 namespace w4a16_tile {
 
 struct Config {
+  bool pair;                   // CTA pairs (w4a16_pair.cu, 256-token tiles) or single CTAs (128-token tiles)
+  int resident_pairs;          // pairs the device can hold at once
   int sm_count;
   int splits;                  // K ranges per tile; more than one needs the workspace
   size_t workspace_bytes;      // splits * m * n floats when splits > 1, else 0
@@ -29,6 +31,12 @@ int prepare(Config* config, int m, int n, int k);
 // 16-byte aligned except the scales (2 bytes). `workspace`: workspace_bytes of device memory.
 int launch(Config* config, cudaStream_t stream, const void* input, const void* weight, const void* scales,
            void* output, void* workspace, int m, int n, int k, uint32_t* status_word);
+
+// The CTA-pair kernel (w4a16_pair.cu): attribute and occupancy at plan creation, launch with the
+// tensor maps of `config` already encoded.
+int prepare_pair(Config* config);
+int launch_pair(Config* config, cudaStream_t stream, const void* scales, void* output, void* workspace, int m,
+                int n, int k, uint32_t* status_word);
 
 }  // namespace w4a16_tile
 }  // namespace mircuda_b200

@@ -146,11 +146,12 @@ def test_w4a16_benchmark_shapes(cuda_stream, w4a16_kernel, m, n, k):
     assert_close(out, torch.from_numpy(expected.astype(np.float32)), f"w4a16 {m}x{n}x{k}")
 
 
-@pytest.mark.parametrize("prefill", ["tile", "expand"])
+@pytest.mark.parametrize("prefill", ["fused", "single", "expand"])
 @pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (40, 264, 384), (17, 8, 128), (300, 1000, 2176),
                                    (128, 256, 128), (129, 776, 4096), (64, 264, 8192)])
 def test_w4a16_prefill_kernels(cuda_stream, monkeypatch, prefill, m, n, k):
-    """M > 16: the fused GEMM (packed weights expanded inside the kernel) and the two-launch form
+    """M > 16: the fused GEMM (packed weights expanded inside the kernel; CTA pairs above 128 tokens
+    by default, single CTAs with `single`) and the two-launch form
     (expansion into an f16 workspace, then the dense GEMM), ragged in M and N, one and many scale
     groups along K, with and without K ranges met through fp32 partial sums (the last two
     shapes); both must produce the oracle's product."""
