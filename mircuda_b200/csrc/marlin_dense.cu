@@ -22,11 +22,11 @@
 
 #include <cstdlib>
 #include <cstring>
-#include <mutex>
 
 #include "fp4_codec.cuh"
 #include "launch_overlap.hpp"
 #include "marlin_common.cuh"
+#include "marlin_status.hpp"
 #include "marlin_stream.hpp"
 #include "ptx.cuh"
 
@@ -236,29 +236,12 @@ extern "C" int mircuda_marlin_nvfp4_dense_execute(void* stream, const void* inpu
   }
   if (status != 0) return status;
   // Shapes the streaming kernel covers go to it (MIRCUDA_B200_MARLIN_DENSE=tiles keeps the tile
-  // kernel below). Its bounded waits report through one pinned word per process: a launch whose
-  // wait ran out makes every later call return -3. The word is allocated by the first call that
-  // is not being captured into a graph; until it exists (a first call under capture) the kernel
-  // runs without a place to report to.
+  // kernel below). Its bounded waits report through the process-wide status word.
   const char* choice = std::getenv("MIRCUDA_B200_MARLIN_DENSE");
   if (choice == nullptr || std::strcmp(choice, "tiles") != 0) {
-    static std::mutex guard;
-    static uint32_t* stream_status = nullptr;
-    {
-      std::lock_guard<std::mutex> hold(guard);
-      if (stream_status == nullptr) {
-        cudaStreamCaptureStatus capture = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(static_cast<cudaStream_t>(stream), &capture) == cudaSuccess &&
-            capture == cudaStreamCaptureStatusNone) {
-          void* memory = nullptr;
-          status = static_cast<int>(cudaHostAlloc(&memory, sizeof(uint32_t), cudaHostAllocPortable));
-          if (status != 0) return status;
-          stream_status = static_cast<uint32_t*>(memory);
-          *stream_status = 0u;
-        }
-      }
-    }
-    if (stream_status != nullptr && *reinterpret_cast<volatile uint32_t*>(stream_status) != 0u) return -3;
+    bool failed = false;
+    uint32_t* stream_status = mircuda_b200::marlin_status_word(static_cast<cudaStream_t>(stream), &failed);
+    if (failed) return -3;
     mircuda_b200::marlin_stream::Config config = {};
     if ((reinterpret_cast<uintptr_t>(weight) & 15u) == 0u && (reinterpret_cast<uintptr_t>(scales) & 7u) == 0u &&
         (reinterpret_cast<uintptr_t>(temporary) & 15u) == 0u &&

@@ -22,8 +22,13 @@
 
 #include <cstdint>
 
+#include <cstdlib>
+#include <cstring>
+
 #include "fp4_codec.cuh"
 #include "marlin_common.cuh"
+#include "marlin_moe_stream.hpp"
+#include "marlin_status.hpp"
 
 namespace mircuda_b200 {
 namespace marlin_moe {
@@ -211,6 +216,22 @@ int execute(void* stream, const void* input, const void* weight, void* output, c
   // (src/marlin/spec.rs:100-105).
   const int block_size = thread_config < 3 ? 8 : 64;
   const long long assignments = static_cast<long long>(tokens) * top_k;
+  // Shapes the streaming kernel covers go to it, except short K with few routed rows, where its
+  // per-unit costs outweigh what it streams (K = 768 x N = 2048, one token: 7.3 against 6.2 us).
+  // MIRCUDA_B200_MARLIN_MOE=tiles / stream forces the tile kernel below / the streaming kernel.
+  const char* choice = std::getenv("MIRCUDA_B200_MARLIN_MOE");
+  const bool forced_stream = choice != nullptr && std::strcmp(choice, "stream") == 0;
+  if ((choice == nullptr || forced_stream) && (forced_stream || k >= 1024 || assignments >= 32) &&
+      marlin_moe_stream::eligible(n, k) &&
+      assignments < (1ll << 31) && (reinterpret_cast<uintptr_t>(weight) & 15u) == 0u &&
+      (reinterpret_cast<uintptr_t>(scales) & 7u) == 0u) {
+    bool failed = false;
+    uint32_t* status_word = marlin_status_word(static_cast<cudaStream_t>(stream), &failed);
+    if (failed) return -3;
+    return marlin_moe_stream::launch(static_cast<cudaStream_t>(stream), MXFP4, block_size, input, weight, scales,
+                                     global_scales, output, sorted, expert_ids, padded, routing, top_k,
+                                     multiply_routing, static_cast<int>(assignments), n, k, status_word);
+  }
   // The padded length is only known on the device; the grid covers its upper bound
   // (assignments + one partly filled block per expert is at most assignments * block_size).
   auto cuda_stream = static_cast<cudaStream_t>(stream);

@@ -116,13 +116,22 @@ def expected_outputs(x, weights, selected, top_k, routing):
     return oracle.f32_to_bf16(np.asarray(rows, dtype=np.float32))
 
 
+@pytest.fixture(params=["stream", "tiles"])
+def moe_kernel(request, monkeypatch):
+    """Both kernels behind the routed entry points: the streaming one (k % 256 == 0, k <= 2048;
+    other shapes fall to the tile kernel) and the tile kernel."""
+    monkeypatch.setenv("MIRCUDA_B200_MARLIN_MOE", request.param)
+    return request.param
+
+
 @pytest.mark.parametrize("thread_config,block_size", [(N64K128, 8), (M64N64K128, 64)])
 @pytest.mark.parametrize("multiply", [False, True])
-def test_nvfp4_moe_random(cuda_stream, thread_config, block_size, multiply):
+@pytest.mark.parametrize("n,k", [(192, 272), (256, 768), (192, 2048), (64, 256)])
+def test_nvfp4_moe_random(cuda_stream, moe_kernel, thread_config, block_size, multiply, n, k):
     from mircuda_b200 import _lib
     library = _lib.load()
     stream = ctypes.c_void_p(cuda_stream.cuda_stream)
-    experts, tokens, top_k, n, k = 5, 37, 2, 192, 272
+    experts, tokens, top_k = 5, 37, 2
     rng = np.random.default_rng(41 + block_size)
     codes = rng.integers(0, 256, size=experts * n * k // 2, dtype=np.uint8)
     scales = rng.integers(0x28, 0x48, size=experts * n * k // 16, dtype=np.uint8)
@@ -164,11 +173,12 @@ def test_nvfp4_moe_random(cuda_stream, thread_config, block_size, multiply):
 
 
 @pytest.mark.parametrize("thread_config,block_size", [(N128K128, 8), (M64N64K128, 64)])
-def test_mxfp4_moe_random(cuda_stream, thread_config, block_size):
+@pytest.mark.parametrize("n,k", [(128, 320), (128, 512), (192, 2048), (256, 768)])
+def test_mxfp4_moe_random(cuda_stream, moe_kernel, thread_config, block_size, n, k):
     from mircuda_b200 import _lib
     library = _lib.load()
     stream = ctypes.c_void_p(cuda_stream.cuda_stream)
-    experts, tokens, top_k, n, k = 3, 21, 3, 128, 320
+    experts, tokens, top_k = 3, 21, 3
     rng = np.random.default_rng(43 + block_size)
     codes = rng.integers(0, 256, size=experts * n * k // 2, dtype=np.uint8)
     scales = rng.integers(118, 132, size=experts * n * k // 32, dtype=np.uint8)
