@@ -358,7 +358,10 @@ int mircuda_b200_moe_collect_rows_bf16(void* const* result_buffers, uint32_t wor
  * `temporary`, `locks`, `atomic_reduce` are accepted for compatibility and not used (no K
  * slicing). Replace sys/native/marlin/moe_kernel.cu:175-205 and mxfp4_moe_kernel.cu:145-171,
  * declared in sys/src/platform/marlin/execute/mod.rs:32-53 and execute/mxfp4.rs:13-34.
- * output_features % 64 == 0; input_features % 16 == 0 (32 for MXFP4). */
+ * output_features % 64 == 0; input_features % 16 == 0 (32 for MXFP4). Shapes with
+ * input_features % 256 == 0 and <= 2048 run on a streaming kernel that converts the activations
+ * bf16 -> f16 (saturating at +-65504); it reads nothing before the kernel in front of it on the
+ * stream has completed. Returns -3 on every call after a launch whose bounded wait ran out. */
 int mircuda_marlin_nvfp4_moe_execute(void* stream, const void* input, const void* weight,
                                      void* output, void* temporary, const void* scales,
                                      const void* global_scales, const void* sorted,
