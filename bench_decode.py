@@ -1,6 +1,6 @@
 """Decode-path micro-benchmarks (bandwidth-bound GEMVs) on one B200.
 
-    python bench_decode.py [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8,marlin_moe]
+    python bench_decode.py [--cycles 200] [--repeats 5] [--ops nvfp4,fp4,dense,marlin,w4a16,scaled_fp8,marlin_moe,fp4_gemm]
 
 Method follows the reference's examples (examples/dense-vector.rs:9,133-141,172-194 and
 examples/fp4-vector.rs:9-11,102-116): for every shape the weights live in enough rotating
@@ -313,6 +313,25 @@ def bench_scaled_fp8(stream, n, k, m, cycles, repeats):
     return seconds, n * k + m * k + m * n * 2 + n * 6 + m * 4, banks
 
 
+def bench_fp4_gemm(stream, n, k, m, cycles, repeats):
+    """NVFP4 x NVFP4 prefill GEMM (mircuda_fp4_*): E2M1 codes and UE4M3 block scales for both
+    operands (random bytes with scales in [2^-2, 4]), bf16 output."""
+    from mircuda_b200 import plans_fp4
+    spec = plans_fp4.BlockScaledFp4Spec(m, n, k)
+    banks = max(2, min(8, _banks(n * k // 2)))
+    weights = [_random_bytes(n * k // 2, 0, 256) for _ in range(banks)]
+    weight_scales = [_random_bytes(spec.scale_bytes(n), 0x28, 0x48) for _ in range(banks)]
+    a = _random_bytes(m * k // 2, 0, 256)
+    a_scales = _random_bytes(spec.scale_bytes(m), 0x28, 0x48)
+    out = torch.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    plan = plans_fp4.BlockScaledFp4Plan(stream, spec)
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: plan.execute(stream, a, a_scales, weights[i], weight_scales[i], out, 1.0),
+                    banks, cycles, repeats)
+    plan.close()
+    return seconds, (n * k + m * k) // 2 + spec.scale_bytes(n) + spec.scale_bytes(m) + m * n * 2, banks
+
+
 def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=None, sampler=None,
         echo: bool = True) -> dict:
     torch.cuda.set_device(0)
@@ -324,7 +343,7 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
             if shapes and name not in shapes:
                 continue
             for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else
-                      [1, 16, 512] if op == "scaled_fp8" else
+                      [1, 16, 512] if op == "scaled_fp8" else [4096] if op == "fp4_gemm" else
                       [1, 8, 64] if op == "marlin_moe" else [1]):
                 if tokens and m not in tokens:
                     continue
@@ -342,13 +361,15 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                         seconds, byte_count, banks = bench_marlin_moe(stream, n, k, m, cycles, repeats)
                     elif op == "scaled_fp8":
                         seconds, byte_count, banks = bench_scaled_fp8(stream, n, k, m, cycles, repeats)
+                    elif op == "fp4_gemm":
+                        seconds, byte_count, banks = bench_fp4_gemm(stream, n, k, m, max(8, cycles // 10), repeats)
                     else:
                         seconds, byte_count, banks = bench_marlin(stream, n, k, m, cycles, repeats)
                 torch.cuda.empty_cache()
                 record = {"op": op, "shape": name, "n": n, "k": k, "m": m, "us": seconds * 1e6,
                           "gbs": byte_count / seconds / 1e9, "frac_of_measured_hbm":
                           byte_count / seconds / 1e9 / peak_gbs, "banks": banks}
-                if op in ("w4a16", "scaled_fp8"):
+                if op in ("w4a16", "scaled_fp8", "fp4_gemm"):
                     record["tflops"] = 2.0 * m * n * k / seconds / 1e12
                 if sampler is not None:
                     clocks = sampler.summary(mark)
