@@ -343,7 +343,7 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
             if shapes and name not in shapes:
                 continue
             for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else
-                      [1, 16, 512] if op == "scaled_fp8" else [4096] if op == "fp4_gemm" else
+                      [1, 16, 512, 4096] if op == "scaled_fp8" else [4096] if op == "fp4_gemm" else
                       [1, 8, 64] if op == "marlin_moe" else [1]):
                 if tokens and m not in tokens:
                     continue

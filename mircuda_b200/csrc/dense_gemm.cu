@@ -16,6 +16,9 @@
 #include <cstdint>
 #include <new>
 
+#include <cstdlib>
+
+#include "dense_pair.cuh"
 #include "dense_tile.cuh"
 #include "ptx.cuh"
 #include "tensor_map.hpp"
@@ -117,9 +120,12 @@ struct Plan {
   const void* cached_a;
   const void* cached_b;
   CUtensorMap map_a, map_b;
+  bool pair;                 // more than 128 rows of A: CTA pairs (dense_pair.cuh)
+  int resident_pairs;
 };
 
 constexpr uint32_t kBlockN = 256, kStages = 4, kAccStages = 2;
+constexpr uint32_t kPairStages = 6;     // a CTA of a pair holds 32 KB per stage
 
 int encode_operand(CUtensorMap* map, const void* base, uint64_t rows, uint64_t k, uint32_t box_rows) {
   return encode_k_major_map(map, base, rows, k, 2u, box_rows);
@@ -160,6 +166,12 @@ extern "C" int mircuda_dense_create(int input_type, int output_type, int m, int 
         cudaFuncAttributeMaxDynamicSharedMemorySize,
         Layout<kBlockN, kStages, kAccStages>::kDynamicBytes));
   }
+  // More than 128 rows of A run on CTA pairs (MIRCUDA_B200_DENSE_PAIR=0 keeps single CTAs).
+  const char* pair_choice = std::getenv("MIRCUDA_B200_DENSE_PAIR");
+  plan->pair = plan->aligned && m > static_cast<int>(kBlockM) && !(pair_choice != nullptr && pair_choice[0] == '0');
+  if (status == 0 && plan->pair) {
+    status = mircuda_b200::dense_pair::prepare<kBlockN, kPairStages, kAccStages, Epilogue>(plan->sm_count, &plan->resident_pairs);
+  }
   if (status != 0) {
     if (plan->status != nullptr) cudaFreeHost(plan->status);
     delete plan;
@@ -195,9 +207,15 @@ extern "C" int mircuda_dense_execute(void* raw, void* stream, const void* a, con
     plan->cached_a = a;
   }
   if (b != plan->cached_b) {
-    const int status = encode_operand(&plan->map_b, b, plan->n, plan->k, kBlockN);
+    const int status = encode_operand(&plan->map_b, b, plan->n, plan->k, plan->pair ? kBlockN / 2u : kBlockN);
     if (status != 0) return status;
     plan->cached_b = b;
+  }
+  if (plan->pair) {
+    return mircuda_b200::dense_pair::launch<kBlockN, kPairStages, kAccStages, Epilogue>(
+        cuda_stream, plan->resident_pairs, plan->map_a, plan->map_b, plan->m, plan->n, plan->k,
+        ptx::make_f16_idesc(plan->input_type == kBf16, 2u * kBlockM, kBlockN),
+        Epilogue{c, plan->output_type, alpha, beta}, plan->status);
   }
   const uint32_t tiles = ((plan->m + kBlockM - 1u) / kBlockM) * ((plan->n + kBlockN - 1u) / kBlockN);
   const uint32_t grid = tiles < static_cast<uint32_t>(plan->sm_count) ? tiles : plan->sm_count;

@@ -158,4 +158,32 @@ __device__ __forceinline__ void mma_nvf4_block16_pair(uint32_t d_tmem, uint64_t 
       : "memory");
 }
 
+// kind::f16 (f16 / bf16 operands) and kind::f8f6f4 without block scales, fp32 accumulator, on a
+// CTA pair: M = 256 rows (128 per CTA), each CTA supplying half of the N rows of B.
+__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_descriptor, uint64_t b_descriptor,
+                                             uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem),
+      "l"(a_descriptor), "l"(b_descriptor), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t a_descriptor, uint64_t b_descriptor,
+                                                uint32_t idesc, bool accumulate) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t"
+      "}\n"
+      ::"r"(d_tmem),
+      "l"(a_descriptor), "l"(b_descriptor), "r"(idesc), "r"(accumulate ? 1u : 0u)
+      : "memory");
+}
+
 }  // namespace mircuda_b200::ptx

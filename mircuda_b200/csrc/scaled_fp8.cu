@@ -21,6 +21,9 @@
 #include <cstdint>
 #include <new>
 
+#include <cstdlib>
+
+#include "dense_pair.cuh"
 #include "dense_tile.cuh"
 #include "fp4_codec.cuh"
 #include "ptx.cuh"
@@ -35,6 +38,7 @@ using dense_tile::kThreads;
 using dense_tile::Layout;
 
 constexpr uint32_t kBlockN = 256, kStages = 4, kAccStages = 2;
+constexpr uint32_t kPairStages = 6;     // a CTA of a pair holds 32 KB per stage
 constexpr int kRowsWarps = 8;
 constexpr int kRowsUnroll = 4;
 
@@ -177,6 +181,8 @@ struct Plan {
   const void* cached_input;
   const void* cached_weight;
   CUtensorMap map_input, map_weight;
+  bool pair;                // more than 128 tokens: CTA pairs (dense_pair.cuh)
+  int resident_pairs;
 };
 
 }  // namespace scaled_fp8
@@ -214,6 +220,12 @@ extern "C" int mircuda_scaled_fp8_create(int m, int n, int k, int scale_type, in
         dense_tile_kernel<kBlockN, kStages, kAccStages, Epilogue>,
         cudaFuncAttributeMaxDynamicSharedMemorySize,
         Layout<kBlockN, kStages, kAccStages>::kDynamicBytes));
+  }
+  // More than 128 tokens run on CTA pairs (MIRCUDA_B200_DENSE_PAIR=0 keeps single CTAs).
+  const char* pair_choice = std::getenv("MIRCUDA_B200_DENSE_PAIR");
+  plan->pair = m > static_cast<int>(kBlockM) && !(pair_choice != nullptr && pair_choice[0] == '0');
+  if (status == 0 && plan->pair) {
+    status = mircuda_b200::dense_pair::prepare<kBlockN, kPairStages, kAccStages, Epilogue>(plan->sm_count, &plan->resident_pairs);
   }
   if (status != 0) {
     if (plan->status != nullptr) cudaFreeHost(plan->status);
@@ -268,9 +280,15 @@ extern "C" int mircuda_scaled_fp8_execute(void* raw, void* stream, const void* i
     plan->cached_input = input;
   }
   if (weight != plan->cached_weight) {
-    const int status = encode_k_major_map(&plan->map_weight, weight, plan->n, plan->k, 1u, kBlockN);
+    const int status = encode_k_major_map(&plan->map_weight, weight, plan->n, plan->k, 1u,
+                                          plan->pair ? kBlockN / 2u : kBlockN);
     if (status != 0) return status;
     plan->cached_weight = weight;
+  }
+  if (plan->pair) {
+    return mircuda_b200::dense_pair::launch<kBlockN, kPairStages, kAccStages, Epilogue>(
+        cuda_stream, plan->resident_pairs, plan->map_input, plan->map_weight, plan->m, plan->n, plan->k,
+        ptx::make_f16_idesc(false, 2u * kBlockM, kBlockN), Epilogue{result, scales}, plan->status);
   }
   const uint32_t tiles = ((plan->m + kBlockM - 1u) / kBlockM) * ((plan->n + kBlockN - 1u) / kBlockN);
   const uint32_t grid = tiles < static_cast<uint32_t>(plan->sm_count) ? tiles : plan->sm_count;

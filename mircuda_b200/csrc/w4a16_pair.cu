@@ -64,19 +64,6 @@ struct Layout {
   static_assert(kDynamicBytes <= 232448, "shared memory budget");
 };
 
-__device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t a_descriptor, uint64_t b_descriptor,
-                                             uint32_t idesc, bool accumulate) {
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t"
-      "}\n"
-      ::"r"(d_tmem),
-      "l"(a_descriptor), "l"(b_descriptor), "r"(idesc), "r"(accumulate ? 1u : 0u)
-      : "memory");
-}
-
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                   const __half* __restrict__ scales, __half* __restrict__ c, float* __restrict__ partial,
@@ -216,7 +203,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_consta
               ptx::make_k_major_sw128_descriptor(ptx::smem_address(shared_b + b_stage * L::kBBytes));
 #pragma unroll
           for (uint32_t kb = 0; kb < 4u; ++kb) {
-            mma_f16_pair(d_tmem, a_descriptor + 2u * kb, b_descriptor + 2u * kb, idesc, (kt | kb) != 0u);
+            ptx::mma_f16_pair(d_tmem, a_descriptor + 2u * kb, b_descriptor + 2u * kb, idesc, (kt | kb) != 0u);
           }
           // Both CTAs' activation tiles and expanded half-tiles of the stage are free again.
           ptx::tcgen05_commit_pair(&empty[stage], 3u);
