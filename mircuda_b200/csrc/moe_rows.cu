@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(kThreads)
 moe_swiglu_kernel(const uint4* __restrict__ input, uint4* __restrict__ output, uint32_t rows,
                   const unsigned int* __restrict__ row_bound,
                   uint32_t pieces) {   // pieces = intermediate / 8
+  ptx::dependency_launch_next();
+  ptx::dependency_wait();
   if (row_bound != nullptr) rows = min(rows, __ldg(row_bound));
   const size_t total = static_cast<size_t>(rows) * pieces;
   for (size_t item = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; item < total;
@@ -204,7 +206,9 @@ moe_dispatch_rows_kernel(const uint4* __restrict__ source, const int* __restrict
   for (uint32_t item = blockIdx.x * (kThreads / 32) + threadIdx.x / 32u; item < count; item += warps) {
     const int expert = __ldg(sorted_expert + item);
     const uint32_t owner = static_cast<uint32_t>(expert) / local_experts;
-    const int row = __ldg(base_for_me + expert) + __ldg(position + item);
+    // An expert index outside the job (no such owner) is treated like a row that does not fit.
+    const bool known = expert >= 0 && owner < 8u && receive.base[owner] != nullptr;
+    const int row = known ? __ldg(base_for_me + expert) + __ldg(position + item) : -1;
     // A row at or past the owner's capacity is not sent (the layout kernel has raised the
     // overflow word and the owner computes nothing for it); -1 tells the way back to skip it.
     if (row < 0 || static_cast<uint32_t>(row) >= capacity_rows) {
@@ -245,14 +249,21 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
     float my_weight = 0.0f;
     if (lane < top_k) {
       const int item = __ldg(slot + token * top_k + lane);
-      const uint32_t owner = static_cast<uint32_t>(__ldg(sorted_expert + item)) / local_experts;
-      const int row = remote_row[item];
-      if (row >= 0) {       // a row that did not fit the owner's buffer contributes nothing
-        my_row = static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(row) * pieces;
-        my_weight = __ldg(weights + token * top_k + lane);
+      if (item >= 0 && static_cast<uint32_t>(item) < tokens * top_k) {
+        const uint32_t owner = static_cast<uint32_t>(__ldg(sorted_expert + item)) / local_experts;
+        const int row = remote_row[item];
+        // a row that did not fit the owner's buffer contributes nothing
+        if (row >= 0 && owner < 8u && results.base[owner] != nullptr) {
+          my_row = static_cast<const uint4*>(results.base[owner]) + static_cast<size_t>(row) * pieces;
+          my_weight = __ldg(weights + token * top_k + lane);
+        }
       }
     }
-    for (uint32_t piece = first_piece + lane; piece < end_piece; piece += 32u) {
+    // Every lane runs the same number of rounds (the shuffles below need the whole warp); lanes
+    // past the end of the run load and store nothing.
+    for (uint32_t round = first_piece; round < end_piece; round += 32u) {
+      const uint32_t piece = round + lane;
+      const bool active = piece < end_piece;
       uint4 values[TOP_K];
       float scale[TOP_K];
 #pragma unroll
@@ -260,8 +271,9 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
         const uint4* row = reinterpret_cast<const uint4*>(
             __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(my_row), choice));
         scale[choice] = __shfl_sync(0xffffffffu, my_weight, choice);
-        values[choice] = (static_cast<uint32_t>(choice) < top_k && row != nullptr) ? row[piece]
-                                                                                   : make_uint4(0u, 0u, 0u, 0u);
+        values[choice] = (active && static_cast<uint32_t>(choice) < top_k && row != nullptr)
+                             ? row[piece]
+                             : make_uint4(0u, 0u, 0u, 0u);
       }
       float sums[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
@@ -274,9 +286,11 @@ moe_collect_rows_kernel(const PeerBases results, const int* __restrict__ slot,
           sums[2 * word + 1] = fmaf(scale[choice], pair.y, sums[2 * word + 1]);
         }
       }
-      output[static_cast<size_t>(token) * pieces + piece] =
-          make_uint4(pack(sums[0], sums[1]), pack(sums[2], sums[3]), pack(sums[4], sums[5]),
-                     pack(sums[6], sums[7]));
+      if (active) {
+        output[static_cast<size_t>(token) * pieces + piece] =
+            make_uint4(pack(sums[0], sums[1]), pack(sums[2], sums[3]), pack(sums[4], sums[5]),
+                       pack(sums[6], sums[7]));
+      }
     }
   }
 }

@@ -104,6 +104,8 @@ class ExpertWeights:
         self.nvfp4 = nvfp4
         self.fused = False
         if nvfp4:
+            # The banks were produced on the caller's current stream; the quantiser runs on `stream`.
+            stream.wait_stream(torch.cuda.current_stream(self.gate_up.device))
             # One quantiser pass per bank: every matrix has a whole number of 128-row scale
             # tiles, so the bank's scale layout is the concatenation of the matrices' layouts.
             for name, bank in (("gate_up", self.gate_up), ("down", self.down)):
@@ -121,7 +123,11 @@ class ExpertWeights:
                 # bank's codes and scales are those of the plain bank, permuted
                 gate = self.gate_up[:, :intermediate].reshape(local_experts, intermediate // 16, 16, k)
                 up = self.gate_up[:, intermediate:].reshape(local_experts, intermediate // 16, 16, k)
-                interleaved = torch.cat([gate, up], dim=2).reshape(local_experts * two_i, k).contiguous()
+                # built on the quantiser's stream, after whatever produced the bank, so that the
+                # temporary's memory is not handed out again while the quantiser still reads it
+                stream.wait_stream(torch.cuda.current_stream(self.gate_up.device))
+                with torch.cuda.stream(stream):
+                    interleaved = torch.cat([gate, up], dim=2).reshape(local_experts * two_i, k).contiguous()
                 codes, scales, global_scale = plans.nvfp4_quantize_bf16(stream, interleaved)
                 self.gate_up_fused_codes, self.gate_up_fused_scales = codes.reshape(-1), scales
                 self.gate_up_fused_global = global_scale
@@ -368,6 +374,8 @@ class ExpertParallelMoe:
         routing is given, one step is run with the intermediate activations' scale measured
         from the data; that scale times `margin` is then frozen too, which lets later steps fuse
         SwiGLU with the quantiser and skip the amax pass."""
+        # set-up time: order the layer's stream after the stream that produced x and the routing
+        self.stream.wait_stream(torch.cuda.current_stream(x.device))
         with torch.cuda.stream(self.stream):
             amax = x.abs().max().float().reshape(1)
             if self.world > 1:
