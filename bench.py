@@ -255,6 +255,10 @@ def run_gpu(args) -> None:
     # multicast address instead of once per rank. Measured at 4 GPUs it is 5 % slower than the
     # per-rank stores (the receiving side, not this GPU's egress, is the limit), so it is opt-in.
     use_multicast = os.environ.get("MIRCUDA_B200_GATHER", "peer") == "multimem"
+    # MIRCUDA_B200_GATHER=copy: the GEMM writes the rank's own full-width buffer only and the copy
+    # engines send each finished column block to the peers while the next layer computes.
+    copier = (gather.ColumnCopier(world, rank)
+              if fused and os.environ.get("MIRCUDA_B200_GATHER", "peer") == "copy" else None)
     multicast_active = bool(fused and use_multicast and all(layer["full"].multicast for layer in layers))
 
     def one_step(record: bool):
@@ -265,7 +269,10 @@ def run_gpu(args) -> None:
             if record:
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record(stream)
-            if fused:
+            if copier is not None:
+                copier.execute(op.plan, stream, op.scratch.quantized_input, op.scratch.input_scales,
+                               layer["codes"], layer["scales"], layer["full"], layer["begin"], layer["end"])
+            elif fused:
                 gather.execute_gather(op.plan, stream, op.scratch.quantized_input,
                                       op.scratch.input_scales, layer["codes"], layer["scales"],
                                       layer["full"], layer["begin"], use_multicast)
@@ -279,7 +286,9 @@ def run_gpu(args) -> None:
                 with torch.cuda.stream(stream):
                     dist.all_gather_into_tensor(layer["gathered"], layer["out"])
         if fused:
-            # The step ends when every rank's stores have landed everywhere.
+            # The step ends when every rank's stores (or copies) have landed everywhere.
+            if copier is not None:
+                copier.join(stream)
             with torch.cuda.stream(stream):
                 layers[-1]["full"].barrier()
 
@@ -383,9 +392,15 @@ def run_gpu(args) -> None:
                 if fused:
                     plans.mxfp8_quantize_bf16(stream, layer["x"], op.scratch.quantized_input,
                                               op.scratch.input_scales)
-                    gather.execute_gather(op.plan, stream, op.scratch.quantized_input,
-                                          op.scratch.input_scales, layer["codes"], layer["scales"],
-                                          layer["full"], layer["begin"], use_multicast)
+                    if copier is not None:
+                        copier.execute(op.plan, stream, op.scratch.quantized_input, op.scratch.input_scales,
+                                       layer["codes"], layer["scales"], layer["full"], layer["begin"],
+                                       layer["end"])
+                        copier.join(stream)
+                    else:
+                        gather.execute_gather(op.plan, stream, op.scratch.quantized_input,
+                                              op.scratch.input_scales, layer["codes"], layer["scales"],
+                                              layer["full"], layer["begin"], use_multicast)
                     layer["full"].barrier()
                 else:
                     # MxFp8TensorCore.execute: the quantizer and the GEMM, the call a user makes.
@@ -517,7 +532,8 @@ def run_gpu(args) -> None:
                 "peak": NVLINK_GBS_PER_DIRECTION, "unit": "GB/s",
                 "frac": received / (ms_per_step * 1e-3) / 1e9 / NVLINK_GBS_PER_DIRECTION,
                 "traffic": None,
-                "kernel": "block_scaled_pair_gemm_kernel (gather epilogue)",
+                "kernel": ("block_scaled_pair_gemm_kernel + one copy-engine 2-D copy per peer and layer"
+                           if copier is not None else "block_scaled_pair_gemm_kernel (gather epilogue)"),
                 "peak_source": ("nominal NVLink 5 ingress per GPU; measured on this pool: 770 GB/s peer copy, "
                                 "555 GB/s for SM-issued peer stores"),
                 "bytes_received_per_rank_per_step": received,
@@ -555,7 +571,10 @@ def run_gpu(args) -> None:
             "config": {
                 "workload": WORKLOAD, "tokens": TOKENS,
                 "shapes": {name: [n, k] for name, n, k in SHAPES},
-                "parallelism": (f"weight N column-sharded x{world}, all-gather fused into the GEMM "
+                "parallelism": (f"weight N column-sharded x{world}, each finished column block sent to the "
+                                "peers by the copy engines while the next layer computes"
+                                if copier is not None else
+                                f"weight N column-sharded x{world}, all-gather fused into the GEMM "
                                 "epilogue (" + ("multimem stores through NVSwitch multicast"
                                                 if multicast_active else "peer stores over NVLink") + ")"
                                 if fused else

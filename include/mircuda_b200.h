@@ -86,6 +86,21 @@ int mircuda_b200_mxfp8_tc_execute_gather(void* plan, void* stream, const void* a
                                          int output_count, int row_stride, int column_offset,
                                          void* multicast_output);
 
+/* All-gather of column blocks with the copy engines, the alternative to the gather epilogue
+ * above for linears sharded along N (no reference counterpart: the reference is single-GPU).
+ * Every rank holds a full-width [rows, pitch] output in peer-mapped memory (`buffers[p]` is rank
+ * p's, `buffers[rank]` the caller's own) and has written its own column block of it on `stream`.
+ * `send` issues one strided device-to-device copy per peer, on a stream per peer, ordered after
+ * the work `stream` holds at the call; `stream` itself goes on at once. `join` makes `stream` wait
+ * for every copy sent so far; the caller then synchronises the ranks before the gathered outputs
+ * are read or a block is written again. world 2..8. `destroy` drains the copy streams. */
+int mircuda_b200_column_gather_create(uint32_t world, uint32_t rank, void** gather);
+int mircuda_b200_column_gather_send(void* gather, void* const* buffers, uint64_t pitch_bytes,
+                                    uint64_t offset_bytes, uint64_t width_bytes, uint64_t rows,
+                                    void* stream);
+int mircuda_b200_column_gather_join(void* gather, void* stream);
+void mircuda_b200_column_gather_destroy(void* gather);
+
 /* Weight-only MXFP8 (bf16 activations, row-major [n, k/32] E8M0 scales, weights as
  * little-endian u32 words), any token count. Replaces `mircuda_mxfp8_bf16` and
  * `mircuda_mxfp8_bf16_tiled` (kernels/mxfp8.cu:111-217) with their launches in

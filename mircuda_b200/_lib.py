@@ -60,6 +60,11 @@ SIGNATURES.update({
     "mircuda_marlin_prepare_moe_routes": (_i, [_vp] * 8 + [_i, _i, _i]),
     "mircuda_marlin_nvfp4_dense_execute": (_i, [_vp] * 7 + [_i, _i, _i, _i, _vp, _b]),
     "mircuda_b200_mxfp8_tc_execute_gather": (_i, [_vp] * 6 + [_vpp, _i, _i, _i, _vp]),
+    "mircuda_b200_column_gather_create": (_i, [_u32, _u32, _vpp]),
+    "mircuda_b200_column_gather_send": (_i, [_vp, _vpp, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64,
+                                             ctypes.c_uint64, _vp]),
+    "mircuda_b200_column_gather_join": (_i, [_vp, _vp]),
+    "mircuda_b200_column_gather_destroy": (None, [_vp]),
     "mircuda_b200_variable_grouped_bf16_create_indexed": (_i, [_i, _i, _i, _i, _i, _vp, _vpp]),
     "mircuda_b200_variable_grouped_bf16_execute_indexed": (_i, [_vp] * 8 + [_f]),
     "mircuda_b200_moe_scatter_rows_bf16": (_i, [_vp, _vp, _vp, _vp, _u32, _u32, _vp]),

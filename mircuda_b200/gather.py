@@ -1,10 +1,14 @@
-"""Column-sharded linears across the GPUs of one box with the all-gather fused into the GEMM.
+"""Column-sharded linears across the GPUs of one box, with the all-gather of the outputs either
+fused into the GEMM or carried by the copy engines beside it.
 
-Each rank owns a contiguous block of weight rows (`sharding.column_shard`), quantizes the
-replicated activations itself, and its GEMM epilogue stores every output tile straight into
-the full-width output buffer of every rank over NVLink (`mircuda_b200_mxfp8_tc_execute_gather`).
-The full-width buffers live in symmetric memory (`torch.distributed._symmetric_memory`), which
-is only used to obtain the peers' device pointers and a stream-ordered cross-GPU barrier.
+Each rank owns a contiguous block of weight rows (`sharding.column_shard`) and quantizes the
+replicated activations itself. `execute_gather`: the GEMM epilogue stores every output tile
+straight into the full-width output buffer of every rank over NVLink
+(`mircuda_b200_mxfp8_tc_execute_gather`). `ColumnCopier`: the GEMM writes only the rank's own
+full-width buffer and one strided device-to-device copy per peer moves the finished column block
+while the next layer computes (`mircuda_b200_column_gather_*`), which needs no store slots of the
+SMs. The full-width buffers live in symmetric memory (`torch.distributed._symmetric_memory`),
+which is only used to obtain the peers' device pointers and a stream-ordered cross-GPU barrier.
 The reference has no multi-GPU path; the partitioning follows its operand layouts.
 """
 from __future__ import annotations
@@ -61,3 +65,47 @@ def execute_gather(plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
         ctypes.c_void_p(output.multicast if multicast and output.multicast else None))
     if status != 0:
         raise NativeError(int(status))
+
+
+class ColumnCopier:
+    """Sends column blocks of `SymmetricOutput` buffers to every peer with the copy engines."""
+
+    def __init__(self, world: int, rank: int):
+        self._lib = _lib.load()
+        self.world, self.rank = world, rank
+        raw = ctypes.c_void_p()
+        status = self._lib.mircuda_b200_column_gather_create(world, rank, ctypes.byref(raw))
+        if status != 0:
+            raise NativeError(int(status))
+        self._raw = raw
+
+    def execute(self, plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
+                output: SymmetricOutput, begin: int, end: int) -> None:
+        """Run `plan` into columns [begin, end) of this rank's own `output`, then start the
+        copies of that block to the peers; `stream` does not wait for them."""
+        if stream.cuda_stream != plan._stream.cuda_stream:
+            raise StreamMismatch()
+        own = (ctypes.c_void_p * 1)(output.pointers[self.rank])
+        handle = ctypes.c_void_p(stream.cuda_stream)
+        status = self._lib.mircuda_b200_mxfp8_tc_execute_gather(
+            plan._raw, handle, ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(a_scales.data_ptr()),
+            ctypes.c_void_p(b.data_ptr()), ctypes.c_void_p(b_scales.data_ptr()),
+            ctypes.cast(own, ctypes.POINTER(ctypes.c_void_p)), 1, output.columns, begin, None)
+        if status == 0:
+            status = self._lib.mircuda_b200_column_gather_send(
+                self._raw, ctypes.cast(output.pointers, ctypes.POINTER(ctypes.c_void_p)),
+                output.columns * 2, begin * 2, (end - begin) * 2, output.rows, handle)
+        if status != 0:
+            raise NativeError(int(status))
+
+    def join(self, stream: torch.cuda.Stream) -> None:
+        """`stream` waits for every copy started so far. Follow it with `SymmetricOutput.barrier()`
+        before the gathered outputs are read or a block is computed again."""
+        status = self._lib.mircuda_b200_column_gather_join(self._raw, ctypes.c_void_p(stream.cuda_stream))
+        if status != 0:
+            raise NativeError(int(status))
+
+    def close(self) -> None:
+        if self._raw:
+            self._lib.mircuda_b200_column_gather_destroy(self._raw)
+            self._raw = ctypes.c_void_p()

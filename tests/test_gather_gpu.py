@@ -55,6 +55,25 @@ def _worker(rank, world, port, results):
             ok = ok and (not np.isnan(oracle.bf16_to_f32(actual)).any()
                          and stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3)
             dist.barrier()
+        # The same gather carried by the copy engines: the GEMM writes the rank's own buffer only
+        # and one strided copy per peer moves the finished block.
+        copier = gather.ColumnCopier(world, rank)
+        for _ in range(2):
+            output = gather.SymmetricOutput(m, n, torch.device("cuda", rank))
+            output.local.fill_(float("nan"))
+            torch.cuda.synchronize()
+            dist.barrier()
+            with torch.cuda.stream(stream):
+                copier.execute(plan, stream, a_codes, a_scales, b_codes, b_scales, output, begin, end)
+                copier.join(stream)
+                output.barrier()
+            stream.synchronize()
+            actual = bf16_bits(output.matrix())
+            stats = oracle.compare_bf16(actual, expected)
+            ok = ok and (not np.isnan(oracle.bf16_to_f32(actual)).any()
+                         and stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3)
+            dist.barrier()
+        copier.close()
         results[rank] = (ok, bool(output.multicast))
     finally:
         dist.destroy_process_group()
