@@ -310,7 +310,9 @@ class ExpertParallelMoe:
     def forward(self, x: torch.Tensor, dispatch: Dispatch, routing_weights: torch.Tensor) -> torch.Tensor:
         """x [tokens, hidden] bf16 on this rank -> output [tokens, hidden] bf16. An overflow of
         the receive capacity seen on an earlier step raises `CapacityExceeded` here; `check()`
-        reports the current one."""
+        reports the current one. Everything is enqueued on the layer's stream and nothing waits
+        for other streams: inputs produced elsewhere must be ordered before this call by the
+        caller (`stream.wait_stream(...)`), as with the plans."""
         self.check(synchronize=False)
         if self.peer:
             return self._forward_peer(x, dispatch, routing_weights)

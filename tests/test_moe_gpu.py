@@ -342,6 +342,52 @@ def test_dispatch_respects_the_receive_capacity(cuda_stream):
     assert int(overflow) == 0 and rows.tolist() == counts
 
 
+def test_dispatch_and_collect_skip_indices_outside_the_job(cuda_stream):
+    """An expert index with no owner, a negative one and a slot past the assignments are treated
+    like rows that did not fit: nothing is stored or loaded for them. The row width (40 pieces of
+    16 bytes) is not a whole number of 32-lane rounds, so the last round of the collection has
+    idle lanes."""
+    import ctypes
+    from mircuda_b200 import _lib
+    library = _lib.load()
+    experts, columns, capacity = 4, 320, 16
+    p = lambda tensor: ctypes.c_void_p(tensor.data_ptr())
+    handle = ctypes.c_void_p(cuda_stream.cuda_stream)
+    i32 = lambda values: torch.tensor(values, dtype=torch.int32, device="cuda")
+    sorted_expert = i32([0, 1, 99, -3, 2, 3])                 # 99: owner 24 of 1; -3: no expert
+    position = i32([0, 0, 0, 0, 0, 0])
+    base_for_me = i32([0, 1, 2, 3])
+    assignments = 6
+    source_index = torch.arange(assignments, dtype=torch.int32, device="cuda")
+    source = (torch.arange(assignments * columns, dtype=torch.float32, device="cuda") % 199 + 1)
+    source = source.view(assignments, columns).to(torch.bfloat16)
+    receive = torch.full((capacity, columns), -7.0, dtype=torch.bfloat16, device="cuda")
+    remote_row = i32([0] * assignments)
+    pointers = (ctypes.c_void_p * 1)(receive.data_ptr())
+    torch.cuda.synchronize()
+    assert library.mircuda_b200_moe_dispatch_rows_bf16(
+        p(source), p(source_index), p(sorted_expert), p(position), p(base_for_me),
+        ctypes.cast(pointers, ctypes.POINTER(ctypes.c_void_p)), 1, p(remote_row), assignments, experts,
+        columns, capacity, handle) == 0
+    cuda_stream.synchronize()
+    assert remote_row.tolist() == [0, 1, -1, -1, 2, 3]
+    assert torch.equal(receive[:4], source[[0, 1, 4, 5]])
+    assert (receive[4:] == -7.0).all()
+    # The way back: three tokens of two choices; token 1 owns the two skipped rows, token 2's second
+    # slot points past the assignments.
+    tokens, top_k = 3, 2
+    slot = i32([0, 1, 2, 3, 4, 1000])
+    weights = torch.full((tokens, top_k), 0.5, dtype=torch.float32, device="cuda")
+    output = torch.full((tokens, columns), float("nan"), dtype=torch.bfloat16, device="cuda")
+    assert library.mircuda_b200_moe_collect_rows_bf16(
+        ctypes.cast(pointers, ctypes.POINTER(ctypes.c_void_p)), 1, p(slot), p(sorted_expert), p(remote_row),
+        p(weights), p(output), tokens, top_k, experts, columns, handle) == 0
+    cuda_stream.synchronize()
+    rows = source.float()
+    expected = torch.stack([0.5 * (rows[0] + rows[1]), torch.zeros(columns, device="cuda"), 0.5 * rows[4]])
+    assert torch.equal(output.float(), expected.to(torch.bfloat16).float())
+
+
 def test_layer_reports_an_exceeded_capacity(cuda_stream):
     """The layer turns the device-side overflow word into CapacityExceeded and stays usable."""
     from mircuda_b200 import moe
