@@ -257,8 +257,18 @@ def run_gpu(args) -> None:
     use_multicast = os.environ.get("MIRCUDA_B200_GATHER", "peer") == "multimem"
     # MIRCUDA_B200_GATHER=copy: the GEMM writes the rank's own full-width buffer only and the copy
     # engines send each finished column block to the peers while the next layer computes.
-    copier = (gather.ColumnCopier(world, rank)
-              if fused and os.environ.get("MIRCUDA_B200_GATHER", "peer") == "copy" else None)
+    # MIRCUDA_B200_GATHER=blocks: the copy engines again, with the gathered result in rank-major
+    # blocks ([world, TOKENS, N / world], what an all-gather call returns) so that every copy is
+    # contiguous; the quantizer of a following layer reads that layout in place.
+    gather_mode = os.environ.get("MIRCUDA_B200_GATHER", "peer")
+    copier = gather.ColumnCopier(world, rank) if fused and gather_mode in ("copy", "blocks") else None
+    blocked = copier is not None and gather_mode == "blocks"
+    if blocked:
+        for layer in layers:
+            if layer["local_n"] * world != layer["n"]:
+                raise SystemExit("MIRCUDA_B200_GATHER=blocks needs equal shards")
+            layer["full"] = gather.SymmetricOutput(world * TOKENS, layer["local_n"], device)
+        torch.cuda.synchronize()
     multicast_active = bool(fused and use_multicast and all(layer["full"].multicast for layer in layers))
 
     def one_step(record: bool):
@@ -269,7 +279,10 @@ def run_gpu(args) -> None:
             if record:
                 start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 start.record(stream)
-            if copier is not None:
+            if blocked:
+                copier.execute_blocks(op.plan, stream, op.scratch.quantized_input, op.scratch.input_scales,
+                                      layer["codes"], layer["scales"], layer["full"])
+            elif copier is not None:
                 copier.execute(op.plan, stream, op.scratch.quantized_input, op.scratch.input_scales,
                                layer["codes"], layer["scales"], layer["full"], layer["begin"], layer["end"])
             elif fused:
@@ -392,7 +405,12 @@ def run_gpu(args) -> None:
                 if fused:
                     plans.mxfp8_quantize_bf16(stream, layer["x"], op.scratch.quantized_input,
                                               op.scratch.input_scales)
-                    if copier is not None:
+                    if blocked:
+                        copier.execute_blocks(op.plan, stream, op.scratch.quantized_input,
+                                              op.scratch.input_scales, layer["codes"], layer["scales"],
+                                              layer["full"])
+                        copier.join(stream)
+                    elif copier is not None:
                         copier.execute(op.plan, stream, op.scratch.quantized_input, op.scratch.input_scales,
                                        layer["codes"], layer["scales"], layer["full"], layer["begin"],
                                        layer["end"])
@@ -414,8 +432,9 @@ def run_gpu(args) -> None:
                 if fused:
                     # Each rank reads back its own column block of the gathered result; only
                     # this rank's GEMM writes those columns.
-                    out_host.view(TOKENS, layer["local_n"]).copy_(
-                        layer["full"].matrix()[:, layer["begin"]:layer["end"]], non_blocking=True)
+                    own = (layer["full"].matrix()[rank * TOKENS:(rank + 1) * TOKENS] if blocked
+                           else layer["full"].matrix()[:, layer["begin"]:layer["end"]])
+                    out_host.view(TOKENS, layer["local_n"]).copy_(own, non_blocking=True)
                 else:
                     out_host.copy_(layer["out"], non_blocking=True)
                 out_free[index].record(copy_out)
@@ -532,7 +551,9 @@ def run_gpu(args) -> None:
                 "peak": NVLINK_GBS_PER_DIRECTION, "unit": "GB/s",
                 "frac": received / (ms_per_step * 1e-3) / 1e9 / NVLINK_GBS_PER_DIRECTION,
                 "traffic": None,
-                "kernel": ("block_scaled_pair_gemm_kernel + one copy-engine 2-D copy per peer and layer"
+                "kernel": ("block_scaled_pair_gemm_kernel + one contiguous copy-engine copy per peer and layer"
+                           if blocked else
+                           "block_scaled_pair_gemm_kernel + one copy-engine 2-D copy per peer and layer"
                            if copier is not None else "block_scaled_pair_gemm_kernel (gather epilogue)"),
                 "peak_source": ("nominal NVLink 5 ingress per GPU; measured on this pool: 770 GB/s peer copy, "
                                 "555 GB/s for SM-issued peer stores"),
@@ -571,7 +592,11 @@ def run_gpu(args) -> None:
             "config": {
                 "workload": WORKLOAD, "tokens": TOKENS,
                 "shapes": {name: [n, k] for name, n, k in SHAPES},
-                "parallelism": (f"weight N column-sharded x{world}, each finished column block sent to the "
+                "parallelism": (f"weight N column-sharded x{world}, outputs all-gathered into rank-major blocks "
+                                f"[{world}, tokens, N/{world}]: each rank's finished block goes to the peers as "
+                                "one contiguous copy-engine copy per peer while the next layer computes"
+                                if blocked else
+                                f"weight N column-sharded x{world}, each finished column block sent to the "
                                 "peers by the copy engines while the next layer computes"
                                 if copier is not None else
                                 f"weight N column-sharded x{world}, all-gather fused into the GEMM "

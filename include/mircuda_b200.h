@@ -47,6 +47,15 @@ unsigned int mircuda_cutlass_version(void);
 int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output, void* scales,
                                      uint32_t rows, uint32_t columns, void* stream);
 
+/* The same quantizer reading its input as column blocks stored one after another: block b is a
+ * contiguous [rows, block_columns] bf16 matrix with columns b * block_columns .. of every row,
+ * the rank-major layout an all-gather of column shards produces (no reference counterpart).
+ * Codes and scales come out exactly as for the row-major input. block_columns % 8 == 0 and
+ * columns % block_columns == 0. */
+int mircuda_b200_mxfp8_quantize_bf16_blocks(const void* input, void* output, void* scales,
+                                            uint32_t rows, uint32_t columns,
+                                            uint32_t block_columns, void* stream);
+
 /* Row-major [rows, columns] E8M0 scales -> swizzled padded layout (one-time weight prep).
  * Replaces `mircuda_mxfp8_swizzle_scales` (kernels/mxfp8.cu:98-109) and its launch in
  * src/mxfp8/tensor_core.rs:89-107. `output` must be zero-filled by the caller. */
@@ -93,7 +102,9 @@ int mircuda_b200_mxfp8_tc_execute_gather(void* plan, void* stream, const void* a
  * `send` issues one strided device-to-device copy per peer, on a stream per peer, ordered after
  * the work `stream` holds at the call; `stream` itself goes on at once. `join` makes `stream` wait
  * for every copy sent so far; the caller then synchronises the ranks before the gathered outputs
- * are read or a block is written again. world 2..8. `destroy` drains the copy streams. */
+ * are read or a block is written again. With rows == 1 or width == pitch the block is contiguous
+ * (the rank-major layout of an all-gather: rank r's [rows, local columns] matrix at block r of
+ * every buffer) and is sent as a 1-D copy. world 2..8. `destroy` drains the copy streams. */
 int mircuda_b200_column_gather_create(uint32_t world, uint32_t rank, void** gather);
 int mircuda_b200_column_gather_send(void* gather, void* const* buffers, uint64_t pitch_bytes,
                                     uint64_t offset_bytes, uint64_t width_bytes, uint64_t rows,

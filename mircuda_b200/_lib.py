@@ -22,6 +22,7 @@ SIGNATURES = {
     "mircuda_b200_version": (_u32, []),
     "mircuda_cutlass_version": (_u32, []),
     "mircuda_b200_mxfp8_quantize_bf16": (_i, [_vp, _vp, _vp, _u32, _u32, _vp]),
+    "mircuda_b200_mxfp8_quantize_bf16_blocks": (_i, [_vp, _vp, _vp, _u32, _u32, _u32, _vp]),
     "mircuda_b200_mxfp8_swizzle_scales": (_i, [_vp, _vp, _u32, _u32, _vp]),
     "mircuda_mxfp8_tc_create": (_i, [_i, _i, _i, _vp, _vpp]),
     "mircuda_mxfp8_tc_workspace_bytes": (_sz, [_vp]),

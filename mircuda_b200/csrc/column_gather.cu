@@ -7,8 +7,10 @@
 // layer overlaps the kernels of the next and takes no store slots of the SMs. `join` makes the
 // compute stream wait for every copy issued so far; the caller then synchronises the ranks
 // (a stream-ordered barrier) before anything reads the gathered outputs or overwrites a block
-// that may still be in flight. One plain asynchronous 2-D copy per peer and call; nothing here
-// waits on the host.
+// that may still be in flight. The same calls carry the other layout of an all-gather, rank-major
+// blocks (rank r's [rows, local columns] matrix at block r of every buffer): a block is contiguous
+// and goes as a 1-D copy, which the engines move faster than narrow row segments. One plain
+// asynchronous copy per peer and call; nothing here waits on the host.
 #include <cuda_runtime_api.h>
 
 #include <cstdint>
@@ -67,17 +69,19 @@ extern "C" int mircuda_b200_column_gather_create(uint32_t world, uint32_t rank, 
   return 0;
 }
 
-// buffers[p]: rank p's full-width output as mapped into this process (buffers[rank] is the own
-// one); the block is `rows` rows of `width_bytes` starting `offset_bytes` into every row of
-// `pitch_bytes`.
+// buffers[p]: rank p's output buffer as mapped into this process (buffers[rank] is the own one);
+// the block is `rows` rows of `width_bytes`, `pitch_bytes` apart, the first starting
+// `offset_bytes` into the buffer: a column block of a full-width matrix, or (one row, or rows
+// that follow one another) a contiguous piece, which is sent with a 1-D copy.
 extern "C" int mircuda_b200_column_gather_send(void* raw, void* const* buffers, uint64_t pitch_bytes,
                                                uint64_t offset_bytes, uint64_t width_bytes,
                                                uint64_t rows, void* stream) {
   auto* gather = static_cast<Gather*>(raw);
   if (gather == nullptr || buffers == nullptr || stream == nullptr || pitch_bytes == 0 || width_bytes == 0 ||
-      rows == 0 || offset_bytes + width_bytes > pitch_bytes) {
+      rows == 0 || width_bytes > pitch_bytes) {
     return -1;
   }
+  const bool contiguous = rows == 1 || width_bytes == pitch_bytes;
   for (uint32_t peer = 0; peer < gather->world; ++peer) {
     if (buffers[peer] == nullptr) return -1;
   }
@@ -88,9 +92,12 @@ extern "C" int mircuda_b200_column_gather_send(void* raw, void* const* buffers, 
     const uint32_t peer = (gather->rank + step) % gather->world;
     status = static_cast<int>(cudaStreamWaitEvent(gather->streams[peer], gather->ready, 0));
     if (status != 0) break;
-    status = static_cast<int>(cudaMemcpy2DAsync(static_cast<uint8_t*>(buffers[peer]) + offset_bytes, pitch_bytes,
-                                                source, pitch_bytes, width_bytes, rows, cudaMemcpyDefault,
-                                                gather->streams[peer]));
+    uint8_t* destination = static_cast<uint8_t*>(buffers[peer]) + offset_bytes;
+    status = contiguous
+                 ? static_cast<int>(cudaMemcpyAsync(destination, source, width_bytes * rows, cudaMemcpyDefault,
+                                                    gather->streams[peer]))
+                 : static_cast<int>(cudaMemcpy2DAsync(destination, pitch_bytes, source, pitch_bytes, width_bytes,
+                                                      rows, cudaMemcpyDefault, gather->streams[peer]));
   }
   gather->pending = true;
   return status;

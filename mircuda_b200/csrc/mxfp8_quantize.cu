@@ -77,10 +77,16 @@ __device__ __forceinline__ uint32_t divide(uint32_t value, const Divisor& d) {
   return static_cast<uint32_t>((static_cast<uint64_t>(value) * d.magic) >> d.shift);
 }
 
-template <bool kPackedScales>
+// kBlockedInput: the [rows, columns] input is stored as column blocks one after another (block b
+// holds columns b * block_columns .. of every row as a contiguous [rows, block_columns] matrix:
+// the rank-major layout an all-gather of column shards produces); `block_row_vectors` and
+// `block_vectors` are block_columns / 8 and rows * block_columns / 8. Outputs are the same as for
+// the row-major input.
+template <bool kPackedScales, bool kBlockedInput = false>
 __global__ void __launch_bounds__(kThreads)
 mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ output,
-                      uint8_t* __restrict__ scales, uint32_t vectors, Divisor groups_per_row) {
+                      uint8_t* __restrict__ scales, uint32_t vectors, Divisor groups_per_row,
+                      uint32_t block_row_vectors = 0u, uint32_t block_vectors = 0u) {
   const uint32_t first = blockIdx.x * (kThreads * kVectorsPerThread) + threadIdx.x;
   // The consumer of the codes (normally the GEMM) may set itself up while this grid runs;
   // this grid waits for everything before it on the stream before its first access.
@@ -91,7 +97,14 @@ mxfp8_quantize_kernel(const uint4* __restrict__ input, uint2* __restrict__ outpu
 #pragma unroll
   for (int item = 0; item < kVectorsPerThread; ++item) {
     const uint32_t vector = first + item * kThreads;
-    values[item] = vector < vectors ? __ldg(input + vector) : make_uint4(0u, 0u, 0u, 0u);
+    uint32_t source = vector;
+    if constexpr (kBlockedInput) {
+      const uint32_t row = divide(vector / 4u, groups_per_row);
+      const uint32_t column_vector = vector - row * (groups_per_row.divisor * 4u);
+      const uint32_t block = column_vector / block_row_vectors;
+      source = block * block_vectors + row * block_row_vectors + (column_vector - block * block_row_vectors);
+    }
+    values[item] = vector < vectors ? __ldg(input + source) : make_uint4(0u, 0u, 0u, 0u);
   }
 
 #pragma unroll
@@ -151,13 +164,17 @@ mxfp8_swizzle_scales_kernel(const uint8_t* __restrict__ input, uint8_t* __restri
 }  // namespace
 }  // namespace mircuda_b200
 
-extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output, void* scales,
-                                                uint32_t rows, uint32_t columns, void* stream) {
-  using namespace mircuda_b200;
+namespace mircuda_b200 {
+namespace {
+
+// block_columns == 0: row-major input.
+int launch_mxfp8_quantize(const void* input, void* output, void* scales, uint32_t rows, uint32_t columns,
+                          uint32_t block_columns, void* stream) {
   if (input == nullptr || output == nullptr || scales == nullptr || stream == nullptr ||
       rows == 0u || columns == 0u || columns % 32u != 0u) {
     return -1;
   }
+  if (block_columns != 0u && (block_columns % 8u != 0u || columns % block_columns != 0u)) return -1;
   if ((reinterpret_cast<uintptr_t>(input) & 15u) != 0u ||
       (reinterpret_cast<uintptr_t>(output) & 7u) != 0u ||
       (reinterpret_cast<uintptr_t>(scales) & 3u) != 0u) {
@@ -184,10 +201,30 @@ extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output,
   attribute.val.programmaticStreamSerializationAllowed = 1;
   config.attrs = &attribute;
   config.numAttrs = overlap_launches() ? 1u : 0u;
-  auto function = columns % 128u == 0u ? mxfp8_quantize_kernel<true> : mxfp8_quantize_kernel<false>;
+  const bool packed = columns % 128u == 0u;
+  const bool blocked = block_columns != 0u && block_columns != columns;
+  auto function = blocked ? (packed ? mxfp8_quantize_kernel<true, true> : mxfp8_quantize_kernel<false, true>)
+                          : (packed ? mxfp8_quantize_kernel<true, false> : mxfp8_quantize_kernel<false, false>);
+  const uint32_t block_row_vectors = blocked ? block_columns / 8u : 0u;
+  const uint32_t block_vectors = blocked ? rows * (block_columns / 8u) : 0u;
   return static_cast<int>(cudaLaunchKernelEx(
       &config, function, static_cast<const uint4*>(input), static_cast<uint2*>(output),
-      static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor));
+      static_cast<uint8_t*>(scales), static_cast<uint32_t>(vectors), divisor, block_row_vectors, block_vectors));
+}
+
+}  // namespace
+}  // namespace mircuda_b200
+
+extern "C" int mircuda_b200_mxfp8_quantize_bf16(const void* input, void* output, void* scales,
+                                                uint32_t rows, uint32_t columns, void* stream) {
+  return mircuda_b200::launch_mxfp8_quantize(input, output, scales, rows, columns, 0u, stream);
+}
+
+extern "C" int mircuda_b200_mxfp8_quantize_bf16_blocks(const void* input, void* output, void* scales,
+                                                       uint32_t rows, uint32_t columns,
+                                                       uint32_t block_columns, void* stream) {
+  if (block_columns == 0u) return -1;
+  return mircuda_b200::launch_mxfp8_quantize(input, output, scales, rows, columns, block_columns, stream);
 }
 
 extern "C" int mircuda_b200_mxfp8_swizzle_scales(const void* input, void* output, uint32_t rows,

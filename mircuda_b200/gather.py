@@ -98,6 +98,23 @@ class ColumnCopier:
         if status != 0:
             raise NativeError(int(status))
 
+    def execute_blocks(self, plan, stream: torch.cuda.Stream, a, a_scales, b, b_scales,
+                       output: SymmetricOutput) -> None:
+        """The rank-major layout of an all-gather: `output` is [world * m, n_local] and rank r's
+        [m, n_local] result is its block r on every rank. Run `plan` into this rank's block of
+        its own `output`, then start one contiguous copy of that block per peer."""
+        if stream.cuda_stream != plan._stream.cuda_stream:
+            raise StreamMismatch()
+        block_rows = output.rows // self.world
+        block_bytes = block_rows * output.columns * 2
+        own = output.matrix()[self.rank * block_rows:(self.rank + 1) * block_rows]
+        plan.execute(stream, a, a_scales, b, b_scales, own.reshape(-1))
+        status = self._lib.mircuda_b200_column_gather_send(
+            self._raw, ctypes.cast(output.pointers, ctypes.POINTER(ctypes.c_void_p)),
+            block_bytes, self.rank * block_bytes, block_bytes, 1, ctypes.c_void_p(stream.cuda_stream))
+        if status != 0:
+            raise NativeError(int(status))
+
     def join(self, stream: torch.cuda.Stream) -> None:
         """`stream` waits for every copy started so far. Follow it with `SymmetricOutput.barrier()`
         before the gathered outputs are read or a block is computed again."""

@@ -147,18 +147,32 @@ class BlockScaledMxFp8Plan:
     __del__ = close
 
 
-def mxfp8_quantize_bf16(stream, values, codes, scales) -> None:
+def mxfp8_quantize_bf16(stream, values, codes, scales, blocks: int = 1) -> None:
     """Launch of the activation quantizer (src/mxfp8/tensor_core.rs:140-158).
 
     ``values`` bf16 [rows, columns]; ``codes`` u8 [rows, columns]; ``scales`` a zero-filled
-    u8 buffer of ``scale_bytes(rows, columns // 32)``.
+    u8 buffer of ``scale_bytes(rows, columns // 32)``. With ``blocks`` > 1 ``values`` is
+    [blocks, rows, columns // blocks]: the column blocks of the matrix one after another, as an
+    all-gather of column shards leaves them; the outputs are those of the row-major matrix.
     """
-    rows, columns = values.shape
+    if blocks > 1:
+        stored_blocks, rows, block_columns = values.shape
+        if stored_blocks != blocks or block_columns % 8 != 0:
+            raise InvalidMatmulShape("blocked input must be [blocks, rows, columns / blocks] with 8-column pieces")
+        columns = blocks * block_columns
+    else:
+        rows, columns = values.shape
     if columns % 32 != 0:
         raise InvalidMatmulShape("columns must be a multiple of 32")
     _exact("MXFP8 codes", rows * columns, codes)
     _exact("MXFP8 scales", scale_bytes(rows, columns // 32), scales)
-    _check(_lib.load().mircuda_b200_mxfp8_quantize_bf16(
+    library = _lib.load()
+    if blocks > 1:
+        _check(library.mircuda_b200_mxfp8_quantize_bf16_blocks(
+            _device_pointer(values, _BF16), _device_pointer(codes, _BYTES),
+            _device_pointer(scales, _BYTES), rows, columns, columns // blocks, _stream_handle(stream)))
+        return
+    _check(library.mircuda_b200_mxfp8_quantize_bf16(
         _device_pointer(values, _BF16), _device_pointer(codes, _BYTES),
         _device_pointer(scales, _BYTES), rows, columns, _stream_handle(stream)))
 

@@ -73,6 +73,31 @@ def _worker(rank, world, port, results):
             ok = ok and (not np.isnan(oracle.bf16_to_f32(actual)).any()
                          and stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3)
             dist.barrier()
+        # Rank-major blocks (what an all-gather call returns): rank r's [m, n / world] result is
+        # block r everywhere, sent as one contiguous copy per peer; the quantizer of a following
+        # layer reads that layout in place.
+        local_n = end - begin
+        blocks = gather.SymmetricOutput(world * m, local_n, torch.device("cuda", rank))
+        blocks.local.fill_(float("nan"))
+        torch.cuda.synchronize()
+        dist.barrier()
+        with torch.cuda.stream(stream):
+            copier.execute_blocks(plan, stream, a_codes, a_scales, b_codes, b_scales, blocks)
+            copier.join(stream)
+            blocks.barrier()
+        stream.synchronize()
+        gathered = blocks.matrix().view(world, m, local_n).permute(1, 0, 2).reshape(m, n)
+        stats = oracle.compare_bf16(bf16_bits(gathered.contiguous()), expected)
+        ok = ok and stats["max_rel_to_max"] <= 1e-2 and stats["rel_frobenius"] <= 5e-3
+        next_codes = torch.empty(m * n, dtype=torch.uint8, device="cuda")
+        next_scales = torch.zeros(plans.scale_bytes(m, n // 32), dtype=torch.uint8, device="cuda")
+        plans.mxfp8_quantize_bf16(stream, blocks.matrix().view(world, m, local_n), next_codes, next_scales,
+                                  blocks=world)
+        stream.synchronize()
+        want_codes, want_scales = oracle.mxfp8_quantize(bf16_bits(gathered.contiguous()))
+        ok = ok and np.array_equal(next_codes.cpu().numpy().reshape(m, n), want_codes)
+        ok = ok and np.array_equal(next_scales.cpu().numpy(), want_scales)
+        dist.barrier()
         copier.close()
         results[rank] = (ok, bool(output.multicast))
     finally:

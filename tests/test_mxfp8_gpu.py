@@ -63,6 +63,25 @@ def test_quantizer_bit_exact_random(cuda_stream, shape):
         assert np.array_equal(scales, reference[1])
 
 
+@pytest.mark.parametrize("shape,blocks", [((128, 1024), 8), ((300, 4096), 4), ((77, 96), 2), ((5, 160), 5),
+                                          ((64, 768), 3)])
+def test_quantizer_blocked_input(cuda_stream, shape, blocks):
+    """Column blocks stored one after another (the layout an all-gather of column shards leaves)
+    give the codes and scales of the row-major matrix, bit for bit."""
+    from mircuda_b200 import plans
+    rows, columns = shape
+    values = seeded_bf16(shape, 1.0, 1700 + rows)
+    blocked = values.view(rows, blocks, columns // blocks).permute(1, 0, 2).contiguous()
+    codes = torch.empty(rows * columns, dtype=torch.uint8, device="cuda")
+    scales = torch.zeros(plans.scale_bytes(rows, columns // 32), dtype=torch.uint8, device="cuda")
+    torch.cuda.synchronize()
+    plans.mxfp8_quantize_bf16(cuda_stream, blocked, codes, scales, blocks=blocks)
+    cuda_stream.synchronize()
+    expected_codes, expected_scales = oracle.mxfp8_quantize(bf16_bits(values))
+    assert np.array_equal(codes.cpu().numpy().reshape(rows, columns), expected_codes)
+    assert np.array_equal(scales.cpu().numpy(), expected_scales)
+
+
 def test_quantizer_bit_exact_every_finite_bf16(cuda_stream):
     """Every finite bf16 value as the block maximum and as a non-maximal element.
 
