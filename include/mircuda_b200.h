@@ -115,7 +115,10 @@ void mircuda_b200_column_gather_destroy(void* gather);
 /* Weight-only MXFP8 (bf16 activations, row-major [n, k/32] E8M0 scales, weights as
  * little-endian u32 words), any token count. Replaces `mircuda_mxfp8_bf16` and
  * `mircuda_mxfp8_bf16_tiled` (kernels/mxfp8.cu:111-217) with their launches in
- * src/mxfp8/matmul.rs:131-157. input_features % 32 == 0. */
+ * src/mxfp8/matmul.rs:131-157. input_features % 32 == 0. Up to 8 tokens with
+ * input_features % 128 == 0 and output_features % 16 == 0 run on the tensor cores with the
+ * activations converted to f16 (exact for magnitudes from 2^-14 to 65504, saturating above;
+ * MIRCUDA_B200_MXFP8_WEIGHT_ONLY=simt keeps the fp32 kernel, which has no such limit). */
 int mircuda_b200_mxfp8_bf16(const void* input, const void* weight, const void* scales,
                             void* output, uint32_t tokens, uint32_t input_features,
                             uint32_t output_features, void* stream);
