@@ -472,7 +472,7 @@ def run_gpu(args) -> None:
     if world == 1 and not args.no_decode:
         import bench_decode
         with ClockSampler(local_rank) as decode_sampler:
-            everything = bench_decode.run(["nvfp4", "fp4", "marlin", "w4a16", "fp4_gemm"], 200, 5, hbm_peak,
+            everything = bench_decode.run(["nvfp4", "fp4", "marlin", "w4a16", "mxfp8_wo", "fp4_gemm"], 200, 5, hbm_peak,
                                           sampler=decode_sampler, echo=False)["results"]
         results = [record for record in everything if record["op"] == "nvfp4"]
         fp4_results = [record for record in everything if record["op"] == "fp4"]
@@ -502,6 +502,10 @@ def run_gpu(args) -> None:
             "w4a16_results": [{key: record[key] for key in ("shape", "m", "us", "gbs", "frac_of_measured_hbm",
                                                             "banks", "sm_mhz", "tflops") if key in record}
                               for record in everything if record["op"] == "w4a16"],
+            # the weight-only MXFP8 projection (mircuda_b200_mxfp8_bf16; kernels/mxfp8.cu:111-217), M in {1,4,8}
+            "mxfp8_weight_only_results": [{key: record[key] for key in ("shape", "m", "us", "gbs",
+                                                                        "frac_of_measured_hbm", "banks", "sm_mhz")}
+                                          for record in everything if record["op"] == "mxfp8_wo"],
             # the NVFP4 x NVFP4 prefill GEMM (mircuda_fp4_*) at M = 4096 and the same four weight shapes:
             # 20 launches from a graph per repeat, i.e. a burst figure (nominal dense FP4: 9000 TFLOP/s)
             "nvfp4_gemm_results": [{key: record[key] for key in ("shape", "m", "us", "tflops", "sm_mhz")

@@ -194,6 +194,20 @@ def bench_dense(stream, n, k, cycles, repeats):
     return seconds, 2.0 * n * k + 2 * k + 2 * n, banks
 
 
+def bench_mxfp8_weight_only(stream, n, k, m, cycles, repeats):
+    """Weight-only MXFP8 projection (bf16 activations, E4M3 weights, row-major E8M0 scales)."""
+    banks = _banks(n * k + n * k // 32)
+    weights = [_random_bytes(n * k, 0x20, 0x48) for _ in range(banks)]
+    row_scales = [_random_bytes(n * k // 32, 120, 130) for _ in range(banks)]
+    x = torch.randn(m * k, device="cuda").to(torch.bfloat16)
+    out = torch.empty(m * n, dtype=torch.bfloat16, device="cuda")
+    operation = plans.MxFp8Matmul(plans.MxFp8Spec(m, k, n))
+    torch.cuda.synchronize()
+    seconds = _time(stream, lambda i: operation.execute(stream, x, weights[i], row_scales[i], out),
+                    banks, cycles, repeats)
+    return seconds, n * k * (1 + 1 / 32) + m * k * 2 + m * n * 2, banks
+
+
 def bench_marlin(stream, n, k, m, cycles, repeats):
     library = _lib.load()
     banks = _banks(n * k // 2 + n * k // 16)
@@ -342,7 +356,7 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                            else SHAPES):
             if shapes and name not in shapes:
                 continue
-            for m in ([1, 4, 8] if op in ("nvfp4", "marlin") else [1, 16, 256] if op == "w4a16" else
+            for m in ([1, 4, 8] if op in ("nvfp4", "marlin", "mxfp8_wo") else [1, 16, 256] if op == "w4a16" else
                       [1, 16, 512, 4096] if op == "scaled_fp8" else [4096] if op == "fp4_gemm" else
                       [1, 8, 64] if op == "marlin_moe" else [1]):
                 if tokens and m not in tokens:
@@ -363,6 +377,8 @@ def run(ops, cycles: int, repeats: int, peak_gbs: float, shapes=None, tokens=Non
                         seconds, byte_count, banks = bench_scaled_fp8(stream, n, k, m, cycles, repeats)
                     elif op == "fp4_gemm":
                         seconds, byte_count, banks = bench_fp4_gemm(stream, n, k, m, max(8, cycles // 10), repeats)
+                    elif op == "mxfp8_wo":
+                        seconds, byte_count, banks = bench_mxfp8_weight_only(stream, n, k, m, cycles, repeats)
                     else:
                         seconds, byte_count, banks = bench_marlin(stream, n, k, m, cycles, repeats)
                 torch.cuda.empty_cache()

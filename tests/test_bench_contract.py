@@ -69,6 +69,8 @@ def test_cuda_arm_line():
     assert len(decode["fp4_vector_results"]) == 4 and len(decode["marlin_results"]) == 12
     assert {entry["m"] for entry in decode["w4a16_results"]} == {1, 16, 256}
     assert len(decode["nvfp4_gemm_results"]) == 4 and all(entry["tflops"] > 0 for entry in decode["nvfp4_gemm_results"])
+    assert {(entry["shape"], entry["m"]) for entry in decode["mxfp8_weight_only_results"]} == {
+        (shape, m) for shape in ("qkv", "o", "gate_up", "down") for m in (1, 4, 8)}
     # the reference's own kernels beside this library's (present when oracle/_ref was built)
     for entry in record["reference_kernels"]["results"]:
         assert entry["us"] > 0 and entry["reference_us"] > 0
