@@ -51,6 +51,17 @@ def test_argument_validation_needs_no_gpu(library):
     assert library.mircuda_b200_nvfp4_vector_create(9, 16, 64, fake_stream, ctypes.byref(raw)) == -1
     assert library.mircuda_b200_mxfp8_quantize_bf16(None, None, None, 1, 32, fake_stream) == -1
     assert library.mircuda_mxfp8_tc_execute(None, fake_stream, None, None, None, None, None) == -1
+    fake = ctypes.c_void_p(0x1000)
+    assert library.mircuda_b200_mxfp8_quantize_bf16_blocks(fake, fake, fake, 4, 128, 0, fake_stream) == -1
+    assert library.mircuda_b200_mxfp8_quantize_bf16_blocks(fake, fake, fake, 4, 128, 48, fake_stream) == -1
+    assert library.mircuda_b200_mxfp8_quantize_bf16_blocks(fake, fake, fake, 4, 128, 12, fake_stream) == -1
+    assert library.mircuda_b200_column_gather_create(1, 0, ctypes.byref(raw)) == -1
+    assert library.mircuda_b200_column_gather_create(9, 0, ctypes.byref(raw)) == -1
+    assert library.mircuda_b200_column_gather_create(4, 4, ctypes.byref(raw)) == -1
+    assert library.mircuda_b200_column_gather_create(4, 0, None) == -1
+    assert library.mircuda_b200_column_gather_send(None, None, 8, 0, 8, 1, fake_stream) == -1
+    assert library.mircuda_b200_column_gather_join(None, fake_stream) == -1
+    library.mircuda_b200_column_gather_destroy(None)
     assert library.mircuda_mxfp8_tc_workspace_bytes(None) == 0
     library.mircuda_mxfp8_tc_destroy(None)
     library.mircuda_fp4_vector_destroy(None)
