@@ -248,7 +248,8 @@ def test_weight_only_golden(cuda_stream):
 
 
 @pytest.mark.parametrize("tokens,k,n", [(1, 4096, 512), (5, 1024, 300), (3, 96, 17), (5, 1024, 304), (8, 4096, 64),
-                                        (3, 128, 16), (2, 12288, 256), (9, 1024, 64), (7, 1152, 48)])
+                                        (3, 128, 16), (2, 12288, 256), (9, 1024, 64), (7, 1152, 48), (2, 1024, 64),
+                                        (1, 12288, 32)])
 def test_weight_only_random(cuda_stream, tokens, k, n):
     from mircuda_b200 import plans
     w = seeded_bf16((n, k), 0.02, 5000)
