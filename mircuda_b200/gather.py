@@ -123,6 +123,8 @@ class ColumnCopier:
             raise NativeError(int(status))
 
     def close(self) -> None:
-        if self._raw:
+        if getattr(self, "_raw", None):
             self._lib.mircuda_b200_column_gather_destroy(self._raw)
             self._raw = ctypes.c_void_p()
+
+    __del__ = close
