@@ -120,3 +120,24 @@ def test_output_alignment_rule_of_the_gemm_plans():
     plans._require_vector_output("C", 12, shifted)   # scalar store path: no rule
     with pytest.raises(plans.MisalignedOperand):
         plans._require_vector_output("C", 8, shifted)
+
+
+def test_blocked_quantizer_input_is_validated_on_the_host():
+    """The blocked form of the activation quantizer takes [blocks, rows, columns / blocks]; shape
+    errors and buffer lengths are reported before anything is launched."""
+    from mircuda_b200 import plans
+
+    class NoStream:
+        cuda_stream = 0x10
+
+    blocked = torch.zeros(4, 8, 64, dtype=torch.bfloat16)
+    codes = torch.zeros(8 * 256, dtype=torch.uint8)
+    scales = torch.zeros(plans.scale_bytes(8, 256 // 32), dtype=torch.uint8)
+    with pytest.raises(plans.InvalidMatmulShape):
+        plans.mxfp8_quantize_bf16(NoStream(), blocked, codes, scales, blocks=2)        # 4 blocks stored
+    with pytest.raises(plans.InvalidMatmulShape):
+        plans.mxfp8_quantize_bf16(NoStream(), torch.zeros(2, 8, 12, dtype=torch.bfloat16), codes, scales, blocks=2)
+    with pytest.raises(plans.MatmulLengthMismatch):
+        plans.mxfp8_quantize_bf16(NoStream(), blocked, codes[:-1], scales, blocks=4)
+    with pytest.raises(ValueError):                                                    # not device memory
+        plans.mxfp8_quantize_bf16(NoStream(), blocked, codes, scales, blocks=4)
